@@ -1,6 +1,8 @@
 """The cache: per-sequence slots over paged key/value storage, and state.
 
-Each schedule entry of a model may ask for one of two things:
+Each schedule entry of a model may ask for one of two things, or for several of them at
+once (a tuple of requests: a layer whose mixer is made of two, say; its view is the tuple of
+their views, in the same order):
 
 * ``KVRequest`` - keys and values of every position (``window == 0``) or of the
   last ``window`` positions.  Entries with the same (kv_heads, head_dim, window)
@@ -119,6 +121,18 @@ class CacheManager:
         self.groups: List[_KVGroup] = []
         self._views: List[Optional[Union[KVView, StateView]]] = []
         by_key: Dict[Tuple[int, int, int, bool, int], List[int]] = {}
+        # an entry that asks for several things: each is served like an entry's own request, and
+        # the entry's view is the tuple of what they get
+        spans: List[Optional[Tuple[int, int]]] = []
+        flat: List[Optional[Union[KVRequest, StateRequest]]] = []
+        for r in requests:
+            if isinstance(r, (tuple, list)):
+                spans.append((len(flat), len(r)))
+                flat.extend(r)
+            else:
+                spans.append(None)
+                flat.append(r)
+        requests = flat
         for i, r in enumerate(requests):
             if isinstance(r, KVRequest):
                 by_key.setdefault((r.kv_heads, r.head_dim, r.window, bool(r.values),
@@ -146,6 +160,14 @@ class CacheManager:
                 self._views.append(None)
             else:
                 raise TypeError(f"schedule entry {i}: unknown cache request {r!r}")
+        flat_views, self._views, at = self._views, [], 0
+        for span in spans:
+            if span is None:
+                self._views.append(flat_views[at])
+                at += 1
+            else:
+                self._views.append(tuple(flat_views[span[0]:span[0] + span[1]]))
+                at += span[1]
 
     # -- what parts see ---------------------------------------------------
     def view(self, entry: int):

@@ -16,6 +16,7 @@ from typing import Any, Dict, Mapping, Type
 
 from .llama import ConfigError, LlamaConfig
 from .nafezen import NafezenConfig
+from .sedopel import SedopelConfig
 from .tazadra import TazadraConfig
 from .spec import ModelSpec
 
@@ -83,3 +84,4 @@ def spec_from_dir(model_dir: str) -> ModelSpec:
 register_architecture(LlamaConfig.architecture, LlamaConfig)
 register_architecture(NafezenConfig.architecture, NafezenConfig)
 register_architecture(TazadraConfig.architecture, TazadraConfig)
+register_architecture(SedopelConfig.architecture, SedopelConfig)

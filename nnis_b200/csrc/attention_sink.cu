@@ -8,12 +8,18 @@
 //                   `rot` values of every head by position * freq[i], q to a packed buffer, k and
 //                   v into the cache row of the token, sigmoid of the gate's logits.  Every part
 //                   is optional (no norm weights, rot 0, no k/v in the rows, no gate).
+//   qkv_prep_heads  the same step with everything per head: rotation of either pairing (neighbours, or
+//                   value i with value i + rot / 2), then optionally an RMS norm of every q and k head
+//                   by itself (no weight, after the rotation), optionally a number per query head that
+//                   multiplies its q (a temperature of the scores), and `gate_cols` gate logits a token
+//                   (one per head, or one per output value).
 //   attn_sink       one warp per (query token, query head) walks the visible keys 32 at a time with
 //                   an online softmax in float32: score = cap * tanh(scale * q.k / cap) (cap 0: none);
 //                   a query at position p sees keys j <= p with j >= p - window + 1 (window > 0) and
 //                   floor(j / chunk) == floor(p / chunk) (chunk > 0, chunks counted from position 0 of
 //                   the sequence); the denominator also holds exp(sink[head]), which has no key and
-//                   no value; the output is multiplied by gate[token, head].  The key range may be
+//                   no value; the output is multiplied by gate[token, head] (or, with `gate_elems` = dv, value by value
+//                   by gate[token, head, :]).  The key range may be
 //                   cut into slices whose partial records a second kernel merges in order (the sink
 //                   counts in the first slice).
 //   attn_sink_group the same where 2, 3, 4, 6 or 8 query heads share a key/value head: one warp per
@@ -104,6 +110,73 @@ qkv_prep_kernel(const float* __restrict__ a, const float* __restrict__ wq, const
             gate_out[(size_t)n * H + i] = 1.0f / (1.0f + expf(-row[nq + nk + nv + i]));
 }
 
+// A warp per head of q and of k.  pairing 0: values (2i, 2i + 1) turn together; 1: values (i, i + rot / 2).
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_scale,
+                      const float* __restrict__ freq, const int* __restrict__ token_pos,
+                      const int* __restrict__ token_seq, const int* __restrict__ page_table, int table_cols,
+                      T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                      float* __restrict__ gate_out, int H, int G, int dk, int dv, int rot, int pairing,
+                      int norm_heads, int gate_cols, int page_size, float eps) {
+    extern __shared__ float turned[];  // [8 warps][dk]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n = blockIdx.x;
+    const int pos = token_pos[n];
+    if (pos < 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nq = H * dk, nk = G * dk, nv = G * dv;
+    const float* row = a + (size_t)n * (nq + nk + nv + gate_cols);
+    const float p = (float)pos;
+    const int half = rot >> 1;
+    size_t cache_row = 0;
+    if (G) {
+        int page = page_table[(size_t)token_seq[n] * table_cols + pos / page_size];
+        cache_row = (size_t)page * G * page_size + (pos % page_size);
+    }
+    float* buf = turned + (size_t)warp * dk;
+    for (int hh = warp; hh < H + G; hh += 8) {
+        const bool is_q = hh < H;
+        const int h = is_q ? hh : hh - H;
+        const float* src = row + (is_q ? 0 : nq) + (size_t)h * dk;
+        float ss = 0.f;
+        for (int i = lane; i < dk; i += 32) {
+            float x = src[i];
+            if (i < rot) {
+                int f, other;
+                bool first;
+                if (pairing) {
+                    first = i < half;
+                    f = first ? i : i - half;
+                    other = first ? i + half : i - half;
+                } else {
+                    first = (i & 1) == 0;
+                    f = i >> 1;
+                    other = i ^ 1;
+                }
+                const float ang = p * freq[f];
+                const float c = cosf(ang), s = sinf(ang), y = src[other];
+                x = first ? x * c - y * s : x * c + y * s;
+            }
+            buf[i] = x;
+            ss = fmaf(x, x, ss);
+        }
+        float inv = 1.0f;
+        if (norm_heads) inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+        if (is_q && q_scale) inv *= q_scale[h];
+        T* dst = is_q ? q_out + (size_t)n * nq + (size_t)h * dk
+                      : k_cache + (cache_row + (size_t)h * page_size) * dk;
+        for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(buf[i] * inv);  // (a lane reads what it wrote)
+    }
+    for (int i = threadIdx.x; i < nv; i += 256) {
+        const int head = i / dv, within = i - head * dv;
+        v_cache[(cache_row + (size_t)head * page_size) * dv + within] = from_float<T>(row[nq + nk + i]);
+    }
+    for (int i = threadIdx.x; i < gate_cols; i += 256)
+        gate_out[(size_t)n * gate_cols + i] = 1.0f / (1.0f + expf(-row[nq + nk + nv + i]));
+}
+
 // partial record per (token, head, slice): [0] running max, [1] running sum, [2 .. 2 + dv) output
 template <typename T, int R>
 __global__ void __launch_bounds__(128)
@@ -112,7 +185,7 @@ attn_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int* __restrict__ page_table, int table_cols, const float* __restrict__ sink,
                  const float* __restrict__ gate, T* __restrict__ out, float* __restrict__ partial,
                  int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int chunk,
-                 float scale, float cap, int n_splits) {
+                 float scale, float cap, int n_splits, int gate_elems) {
     extern __shared__ float q_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -193,12 +266,13 @@ attn_sink_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     }
     if (n_splits == 1) {
         float inv = l > 0.f ? 1.0f / l : 0.f;
-        if (gate) inv *= gate[(size_t)n * nq + hq];
+        const float* ge = (gate && gate_elems > 1) ? gate + ((size_t)n * nq + hq) * dv : nullptr;
+        if (gate && !ge) inv *= gate[(size_t)n * nq + hq];
         T* o = out + ((size_t)n * nq + hq) * dv;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             int i = lane + 32 * r;
-            if (i < dv) o[i] = from_float<T>(acc[r] * inv);
+            if (i < dv) o[i] = from_float<T>(acc[r] * inv * (ge ? ge[i] : 1.0f));
         }
     } else {
         float* rec = partial + (((size_t)n * nq + hq) * n_splits + split) * (size_t)(dv + 2);
@@ -222,7 +296,7 @@ attn_sink_group_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
                        const int* __restrict__ page_table, int table_cols, const float* __restrict__ sink,
                        const float* __restrict__ gate, T* __restrict__ out, float* __restrict__ partial,
                        int n_tokens, int nq, int nkv, int dk, int dv, int page_size, int window, int chunk,
-                       float scale, float cap, int n_splits) {
+                       float scale, float cap, int n_splits, int gate_elems) {
     extern __shared__ __align__(16) float q_smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -336,12 +410,13 @@ attn_sink_group_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
         const int hq = h0 + g;
         if (n_splits == 1) {
             float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
-            if (gate) inv *= gate[(size_t)n * nq + hq];
+            const float* ge = (gate && gate_elems > 1) ? gate + ((size_t)n * nq + hq) * dv : nullptr;
+            if (gate && !ge) inv *= gate[(size_t)n * nq + hq];
             T* o = out + ((size_t)n * nq + hq) * dv;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
                 int i = lane + 32 * r;
-                if (i < dv) o[i] = from_float<T>(acc[g][r] * inv);
+                if (i < dv) o[i] = from_float<T>(acc[g][r] * inv * (ge ? ge[i] : 1.0f));
             }
         } else {
             float* rec = partial + (((size_t)n * nq + hq) * n_splits + split) * (size_t)(dv + 2);
@@ -362,7 +437,7 @@ attn_sink_group_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, c
 template <typename T>
 __global__ void __launch_bounds__(128)
 attn_sink_merge_kernel(const float* __restrict__ partial, const float* __restrict__ gate, T* __restrict__ out,
-                       int d, int n_splits) {
+                       int d, int n_splits, int gate_elems) {
     __shared__ float share[64];
     pdl_wait();
     pdl_launch_dependents();
@@ -388,7 +463,7 @@ attn_sink_merge_kernel(const float* __restrict__ partial, const float* __restric
         }
         l = warp_sum(l);
         float inv = l > 0.f ? 1.0f / l : 0.f;
-        if (gate) inv *= gate[row];
+        if (gate && gate_elems <= 1) inv *= gate[row];
         share[lane] = ms[0] * inv;
         share[lane + 32] = ms[1] * inv;
     }
@@ -399,6 +474,7 @@ attn_sink_merge_kernel(const float* __restrict__ partial, const float* __restric
             float w = share[s];
             if (w > 0.f) o = fmaf(w, rec[(size_t)s * (d + 2) + 2 + i], o);
         }
+        if (gate && gate_elems > 1) o *= gate[row * d + i];
         out[row * d + i] = from_float<T>(o);
     }
 }
@@ -408,7 +484,7 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
                             const int* token_seq, const int* page_table, int table_cols, const float* sink,
                             const float* gate, void* out, float* partial, int n_tokens, int nq, int nkv, int dk,
                             int dv, int page_size, int window, int chunk, float scale, float cap, int n_splits,
-                            cudaStream_t stream) {
+                            int gate_elems, cudaStream_t stream) {
     cudaError_t e;
     const int group = nq / nkv;
     const size_t group_smem = 4 * (size_t)group * dk * sizeof(float);
@@ -419,7 +495,7 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
     e = launch_dependent(attn_sink_group_kernel<T, R, G>, ggrid, 128, group_smem, stream, (const T*)q, \
                          (const T*)k_cache, (const T*)v_cache, token_pos, token_seq, page_table, table_cols, sink, \
                          gate, (T*)out, partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale, cap, \
-                         n_splits)
+                         n_splits, gate_elems)
 #define NNIS_GROUP_R(G) \
     if (dv <= 32) NNIS_GROUP_CASE(1, G); \
     else if (dv <= 64) NNIS_GROUP_CASE(2, G); \
@@ -435,7 +511,7 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
         if (n_splits > 1) {
             size_t rows = (size_t)n_tokens * nq;
             e = launch_dependent(attn_sink_merge_kernel<T>, (unsigned)rows, 128, 0, stream, (const float*)partial,
-                                 gate, (T*)out, dv, n_splits);
+                                 gate, (T*)out, dv, n_splits, gate_elems);
         }
         return e == cudaSuccess ? NNIS_OK : (int)e;
     }
@@ -444,7 +520,8 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
 #define NNIS_SINK_CASE(R) \
     e = launch_dependent(attn_sink_kernel<T, R>, grid, 128, smem, stream, (const T*)q, (const T*)k_cache, \
                          (const T*)v_cache, token_pos, token_seq, page_table, table_cols, sink, gate, (T*)out, \
-                         partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale, cap, n_splits)
+                         partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale, cap, n_splits, \
+                         gate_elems)
     if (dv <= 32) NNIS_SINK_CASE(1);
     else if (dv <= 64) NNIS_SINK_CASE(2);
     else if (dv <= 128) NNIS_SINK_CASE(4);
@@ -454,7 +531,7 @@ static int launch_attn_sink(const void* q, const void* k_cache, const void* v_ca
     if (n_splits > 1) {
         size_t rows = (size_t)n_tokens * nq;
         e = launch_dependent(attn_sink_merge_kernel<T>, (unsigned)rows, 128, 0, stream, (const float*)partial, gate,
-                             (T*)out, dv, n_splits);
+                             (T*)out, dv, n_splits, gate_elems);
     }
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
@@ -490,26 +567,59 @@ NNIS_API int nnis_qkv_prep(const float* a, const float* wq, const float* wk, con
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
+// a: float32 [n, H dk + G dk + G dv + gate_cols]; q_scale: float32 [H] or null; pairing 0: neighbours,
+// 1: halves; norm_heads: every q and k head divided by its own root mean square after the rotation
+NNIS_API int nnis_qkv_prep_heads(const float* a, const float* q_scale, const float* freq, const int* token_pos,
+                                 const int* token_seq, const int* page_table, int table_cols, void* q_out,
+                                 void* k_cache, void* v_cache, float* gate_out, int n_tokens, int H, int G, int dk,
+                                 int dv, int rot, int pairing, int norm_heads, int gate_cols, int page_size,
+                                 float eps, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0 || G < 0 || dk <= 0 || dv <= 0 || rot < 0 || gate_cols < 0 || !a || !q_out ||
+        !token_pos)
+        return NNIS_ERR_ARGUMENT;
+    if ((rot & 1) || rot > dk || dk > 1024) return NNIS_ERR_UNSUPPORTED;
+    if (rot > 0 && !freq) return NNIS_ERR_ARGUMENT;
+    if (G > 0 && (!k_cache || !v_cache || !page_table || !token_seq || page_size <= 0)) return NNIS_ERR_ARGUMENT;
+    if (gate_cols && !gate_out) return NNIS_ERR_ARGUMENT;
+    const size_t smem = 8 * (size_t)dk * sizeof(float);
+    cudaError_t e;
+    if (dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(qkv_prep_heads_kernel<float>, (unsigned)n_tokens, 256, smem, stream, a, q_scale, freq,
+                             token_pos, token_seq, page_table, table_cols, (float*)q_out, (float*)k_cache,
+                             (float*)v_cache, gate_out, H, G, dk, dv, rot, pairing, norm_heads, gate_cols, page_size,
+                             eps);
+    else if (dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(qkv_prep_heads_kernel<bf16>, (unsigned)n_tokens, 256, smem, stream, a, q_scale, freq,
+                             token_pos, token_seq, page_table, table_cols, (bf16*)q_out, (bf16*)k_cache,
+                             (bf16*)v_cache, gate_out, H, G, dk, dv, rot, pairing, norm_heads, gate_cols, page_size,
+                             eps);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
 // q: [n, nq * dk]; caches [pages, nkv, page, dk] and [pages, nkv, page, dv]; sink: float32 [nq] or
-// null; gate: float32 [n, nq] or null; partial: n * nq * n_splits * (dv + 2) floats when n_splits > 1
+// null; gate: float32 [n, nq] (gate_elems 0 or 1) or [n, nq * dv] (gate_elems = dv) or null; partial:
+// n * nq * n_splits * (dv + 2) floats when n_splits > 1
 NNIS_API int nnis_attention_sink(const void* q, const void* k_cache, const void* v_cache, const int* token_pos,
                                  const int* token_seq, const int* page_table, int table_cols, const float* sink,
                                  const float* gate, void* out, float* partial, int n_tokens, int nq, int nkv,
                                  int dk, int dv, int page_size, int window, int chunk, float scale, float cap,
-                                 int n_splits, int dtype, cudaStream_t stream) {
+                                 int n_splits, int gate_elems, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || table_cols <= 0 || n_splits <= 0 ||
         window < 0 || chunk < 0 || cap < 0.f)
         return NNIS_ERR_ARGUMENT;
     if (dk <= 0 || dv <= 0 || dk > 1024 || dv > 256) return NNIS_ERR_UNSUPPORTED;
     if (nq > 65535 || n_splits > 64) return NNIS_ERR_UNSUPPORTED;
     if (n_splits > 1 && !partial) return NNIS_ERR_ARGUMENT;
+    if (gate_elems > 1 && gate_elems != dv) return NNIS_ERR_ARGUMENT;
     if (dtype == NNIS_DTYPE_F32)
         return launch_attn_sink<float>(q, k_cache, v_cache, token_pos, token_seq, page_table, table_cols, sink, gate,
                                        out, partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale,
-                                       cap, n_splits, stream);
+                                       cap, n_splits, gate_elems, stream);
     if (dtype == NNIS_DTYPE_BF16)
         return launch_attn_sink<bf16>(q, k_cache, v_cache, token_pos, token_seq, page_table, table_cols, sink, gate,
                                       out, partial, n_tokens, nq, nkv, dk, dv, page_size, window, chunk, scale,
-                                      cap, n_splits, stream);
+                                      cap, n_splits, gate_elems, stream);
     return NNIS_ERR_UNSUPPORTED;
 }

@@ -28,7 +28,7 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cach
                      const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
                      const int* __restrict__ seq_count, const int* __restrict__ page_table, int table_cols,
                      const float* __restrict__ sink, const float* __restrict__ gate, bf16* __restrict__ out,
-                     int nq, int nkv, int window, int chunk, float scale, float cap) {
+                     int nq, int nkv, int window, int chunk, float scale, float cap, int gate_elems) {
     constexpr int CH = D / 8, NT = D / 8, KS = D / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [64, D] swizzled
@@ -190,19 +190,26 @@ attn_sink_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cach
     const int ra = warp * 16 + r_lo, rb = ra + 8;
     float inv_a = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
     float inv_b = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
-    if (gate) {
+    const bool by_value = gate && gate_elems > 1;  // a gate per output value: [n, nq * D]
+    if (gate && !by_value) {
         if (ra < rows) inv_a *= gate[(size_t)(row_base + ra) * nq + hq];
         if (rb < rows) inv_b *= gate[(size_t)(row_base + rb) * nq + hq];
     }
 #pragma unroll
     for (int jn = 0; jn < NT; ++jn) {
         int col = hq * D + jn * 8 + c_lo;
-        if (ra < rows)
+        if (ra < rows) {
+            float2 g = by_value ? *reinterpret_cast<const float2*>(gate + (size_t)(row_base + ra) * nq * D + col)
+                                : make_float2(1.f, 1.f);
             *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + ra) * nq * D + col) =
-                pack_bf16(o[jn][0] * inv_a, o[jn][1] * inv_a);
-        if (rb < rows)
+                pack_bf16(o[jn][0] * inv_a * g.x, o[jn][1] * inv_a * g.y);
+        }
+        if (rb < rows) {
+            float2 g = by_value ? *reinterpret_cast<const float2*>(gate + (size_t)(row_base + rb) * nq * D + col)
+                                : make_float2(1.f, 1.f);
             *reinterpret_cast<uint32_t*>(out + (size_t)(row_base + rb) * nq * D + col) =
-                pack_bf16(o[jn][2] * inv_b, o[jn][3] * inv_b);
+                pack_bf16(o[jn][2] * inv_b * g.x, o[jn][3] * inv_b * g.y);
+        }
     }
 }
 
@@ -210,7 +217,7 @@ template <int D>
 static int launch_sink_mma(dim3 grid, cudaStream_t stream, const bf16* q, const bf16* k, const bf16* v,
                            const int* tiles, const int* first_row, const int* start, const int* count,
                            const int* table, int cols, const float* sink, const float* gate, bf16* out, int nq,
-                           int nkv, int window, int chunk, float scale, float cap) {
+                           int nkv, int window, int chunk, float scale, float cap, int gate_elems) {
     size_t smem = ((size_t)kSinkRows * D + (size_t)kSinkStages * 2 * kSinkPage * D) * sizeof(bf16);
     auto kernel = attn_sink_mma_kernel<D>;
     if (smem > 48 * 1024) {
@@ -218,7 +225,7 @@ static int launch_sink_mma(dim3 grid, cudaStream_t stream, const bf16* q, const 
         if (e != cudaSuccess) return (int)e;
     }
     kernel<<<grid, 128, smem, stream>>>(q, k, v, tiles, first_row, start, count, table, cols, sink, gate, out, nq,
-                                        nkv, window, chunk, scale, cap);
+                                        nkv, window, chunk, scale, cap, gate_elems);
     NNIS_RETURN_LAUNCH();
 }
 
@@ -226,12 +233,12 @@ static int launch_sink_mma(dim3 grid, cudaStream_t stream, const bf16* q, const 
 
 // `tiles`: int32 [n_tiles, 2] = (sequence of the batch, first query of the tile within this
 // step's tokens of that sequence), 64 queries a tile.  q [n, nq * d], out [n, nq * d], caches
-// [pages, nkv, 64, d].  Takes d = 64 and 128 with 64-key pages; else NNIS_ERR_UNSUPPORTED.
+// [pages, nkv, 64, d]; gate float32 [n, nq] or, with gate_elems = d, [n, nq * d].  Takes d = 64 and 128 with 64-key pages; else NNIS_ERR_UNSUPPORTED.
 NNIS_API int nnis_attention_sink_mma(const void* q, const void* k_cache, const void* v_cache, const int* tiles,
                                      int n_tiles, const int* seq_first_row, const int* seq_start,
                                      const int* seq_count, const int* page_table, int table_cols,
                                      const float* sink, const float* gate, void* out, int nq, int nkv, int d,
-                                     int page_size, int window, int chunk, float scale, float cap,
+                                     int page_size, int window, int chunk, float scale, float cap, int gate_elems,
                                      cudaStream_t stream) {
     using namespace nnis;
     if (n_tiles <= 0 || nq <= 0 || nkv <= 0 || nq % nkv || table_cols <= 0 || window < 0 || chunk < 0 ||
@@ -244,8 +251,8 @@ NNIS_API int nnis_attention_sink_mma(const void* q, const void* k_cache, const v
     if (d == 64)
         return launch_sink_mma<64>(grid, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tiles,
                                    seq_first_row, seq_start, seq_count, page_table, table_cols, sink, gate,
-                                   (bf16*)out, nq, nkv, window, chunk, scale, cap);
+                                   (bf16*)out, nq, nkv, window, chunk, scale, cap, gate_elems);
     return launch_sink_mma<128>(grid, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, tiles,
                                 seq_first_row, seq_start, seq_count, page_table, table_cols, sink, gate,
-                                (bf16*)out, nq, nkv, window, chunk, scale, cap);
+                                (bf16*)out, nq, nkv, window, chunk, scale, cap, gate_elems);
 }

@@ -10,6 +10,12 @@
 //                    g' = min(g, limit), u' = clamp(u, -limit, limit)
 //   tanh_rows        tanh of float32 rows, rounded once to the operand dtype
 //   softcap_rows     x <- cap * tanh(x / cap), float32 in place (logits)
+//   act_rows         a plain activation of float32 rows, rounded once to the operand dtype:
+//                    gelu with erf, 0.5 z (1 + erf(z / sqrt 2)), or its tanh form,
+//                    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+//   depth_mix        keeps a block's result among the results of the blocks before it and
+//                    replaces the stream by a weighted sum of them all:
+//                    history[terms - 1] = hidden; hidden = sum_j w[j] history[j]
 //
 // Norm statistics, the scale and the sum are float32 in every dtype.
 #include "async_copy.cuh"
@@ -106,9 +112,60 @@ __global__ void softcap_rows_kernel(float* __restrict__ x, size_t count, float c
     if (i < count) x[i] = cap * tanhf(x[i] / cap);
 }
 
+template <typename T>
+__global__ void act_rows_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count, int kind) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float z = x[i];
+    float y;
+    if (kind == 0) y = 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    else y = 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    out[i] = from_float<T>(y);
+}
+
+// history: [terms, count] float32 (term j at j * stride); w: [terms]
+__global__ void depth_mix_kernel(float* __restrict__ hidden, float* __restrict__ history,
+                                 const float* __restrict__ w, size_t count, size_t stride, int terms) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    const float x = hidden[i];
+    history[(size_t)(terms - 1) * stride + i] = x;
+    float sum = 0.f;
+    for (int j = 0; j + 1 < terms; ++j) sum = fmaf(w[j], history[(size_t)j * stride + i], sum);
+    hidden[i] = fmaf(w[terms - 1], x, sum);
+}
+
 }  // namespace nnis
 
 using namespace nnis;
+
+// kind 0: gelu (erf); 1: gelu (tanh form)
+NNIS_API int nnis_act_rows(const float* x, void* out, int out_dtype, long long count, int kind,
+                           cudaStream_t stream) {
+    if (count <= 0 || !x || !out || kind < 0 || kind > 1) return NNIS_ERR_ARGUMENT;
+    unsigned blocks = (unsigned)((count + 255) / 256);
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(act_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)out, (size_t)count, kind);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(act_rows_kernel<bf16>, blocks, 256, 0, stream, x, (bf16*)out, (size_t)count, kind);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+NNIS_API int nnis_depth_mix(float* hidden, float* history, const float* w, long long count, long long stride,
+                            int terms, cudaStream_t stream) {
+    if (count <= 0 || stride < count || terms <= 0 || !hidden || !history || !w) return NNIS_ERR_ARGUMENT;
+    unsigned blocks = (unsigned)((count + 255) / 256);
+    cudaError_t e = launch_dependent(depth_mix_kernel, blocks, 256, 0, stream, hidden, history, w, (size_t)count,
+                                     (size_t)stride, terms);
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
 
 NNIS_API int nnis_cast_rows(const float* x, void* out, int out_dtype, long long count, cudaStream_t stream) {
     if (count <= 0 || !x || !out) return NNIS_ERR_ARGUMENT;

@@ -1082,14 +1082,21 @@ def retention(qkvg: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, state
               seq_count: Optional[torch.Tensor], o_raw: torch.Tensor, out: torch.Tensor, heads: int,
               dim: int, vdim: int, rot_dims: int, eps: float, segments: Optional[torch.Tensor] = None,
               seq_first_segment: Optional[torch.Tensor] = None, seg_state: Optional[torch.Tensor] = None,
-              seg_len: int = 0) -> None:
+              seg_len: int = 0, activation: bool = False, key_scale: Optional[float] = None,
+              norm_weight: Optional[torch.Tensor] = None, gate: str = "silu") -> None:
     """Retention of packed rows [q | k | v | g] from and into the per-slot state
     [slots, heads, dim, vdim] (float32); out [n, heads * vdim] = o / rms(o) * silu(g).
+    ``activation``: q, k and v pass silu as they are read; ``key_scale``: what multiplies k
+    (dim^-1/2 unless given); ``norm_weight`` (float32 [heads * vdim]): one norm over a token's
+    joined heads, times this weight, instead of a norm per head; ``gate``: "silu" or "sigmoid".
     Without ``seq_first_row`` every row is one token of a sequence of its own.  With
     ``segments`` (``retention_segments``) a prompt step's sequences are cut into runs of
     ``seg_len`` tokens that are worked side by side (``retention_takes_segments``)."""
     _cuda(qkvg, freq, decay, state, token_pos, token_seq, seq_slots, seq_first_row, seq_start, seq_count,
-          o_raw, out, segments, seq_first_segment, seg_state)
+          o_raw, out, segments, seq_first_segment, seg_state, norm_weight)
+    _need(gate in ("silu", "sigmoid"), "retention: the gate is silu or sigmoid")
+    _need(norm_weight is None or (norm_weight.dtype == torch.float32 and norm_weight.numel() == heads * vdim),
+          "retention: norm_weight float32 [heads * vdim]")
     n_segments = 0
     if segments is not None:
         n_segments = segments.shape[0]
@@ -1111,7 +1118,9 @@ def retention(qkvg: torch.Tensor, freq: torch.Tensor, decay: torch.Tensor, state
                                  _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_start),
                                  _ptr(seq_count), _ptr(segments), n_segments, _ptr(seq_first_segment), seg_len,
                                  _ptr(seg_state), _ptr(o_raw), _ptr(out), n, units, heads, dim, vdim,
-                                 rot_dims, ctypes.c_float(eps), code_of(out.dtype), _stream()),
+                                 rot_dims, ctypes.c_float(eps), 1 if activation else 0,
+                                 ctypes.c_float(dim ** -0.5 if key_scale is None else key_scale),
+                                 _ptr(norm_weight), 1 if gate == "sigmoid" else 0, code_of(out.dtype), _stream()),
            "retention", 4 if segments is not None else 2)
 
 
@@ -1485,20 +1494,27 @@ def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Ten
              freq: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
              page_table: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
              v_cache: Optional[torch.Tensor], gate_out: Optional[torch.Tensor], heads: int, kv_heads: int,
-             dk: int, dv: int, rot: int, eps: float) -> None:
-    """From float32 rows [q | k | v | gate logits]: norms of q and k over their whole projections,
-    rotation of neighbouring pairs, q packed, k and v into the cache, sigmoid of the gate.
-    ``kv_heads == 0``: the rows hold no keys and values."""
-    _cuda(a, wq, wk, freq, token_pos, token_seq, page_table, q_out, k_cache, v_cache, gate_out)
+             dk: int, dv: int, rot: int, eps: float, pairing: str = "neighbours", head_norm: bool = False,
+             q_scale: Optional[torch.Tensor] = None) -> None:
+    """From float32 rows [q | k | v | gate logits]: norms of q and k, rotation, q packed, k and v into
+    the cache, sigmoid of the gate's logits (``gate_out`` [n, heads] or [n, heads * dv]: as many logits a
+    row).  ``kv_heads == 0``: the rows hold no keys and values.  Two forms: with ``wq``/``wk`` the
+    norms go over the whole projections, before the rotation of neighbouring pairs; with
+    ``head_norm``, ``pairing == "half"``, ``q_scale`` (float32 [heads], a multiplier of each head's
+    q) or a gate per value, everything is per head: the rotation (either pairing), then optionally
+    every head divided by its own root mean square."""
+    _cuda(a, wq, wk, freq, token_pos, token_seq, page_table, q_out, k_cache, v_cache, gate_out, q_scale)
     n = a.shape[0]
-    gated = gate_out is not None
-    _need(a.dtype == torch.float32 and a.shape[1] == heads * dk + kv_heads * (dk + dv) + (heads if gated else 0),
+    gate_cols = 0 if gate_out is None else gate_out.shape[1]
+    _need(gate_cols in (0, heads, heads * dv), "qkv_prep: a gate per head or per value")
+    _need(a.dtype == torch.float32 and a.shape[1] == heads * dk + kv_heads * (dk + dv) + gate_cols,
           "qkv_prep: float32 rows [q | k | v | gate]")
     _need(tuple(q_out.shape) == (n, heads * dk), "qkv_prep: q_out [n, heads * dk]")
     for w, size in ((wq, heads * dk), (wk, kv_heads * dk)):
         _need(w is None or (w.dtype == torch.float32 and w.numel() == size), "qkv_prep: float32 norm weights")
     _need(rot == 0 or (freq is not None and freq.dtype == torch.float32 and freq.numel() >= rot // 2),
           "qkv_prep: freq float32 [rot / 2]")
+    _need(pairing in ("neighbours", "half"), "qkv_prep: pairing is neighbours or half")
     cols, page_size = 0, 1
     if kv_heads:
         _need(k_cache.dtype == v_cache.dtype == q_out.dtype and tuple(k_cache.shape[1:3]) == tuple(v_cache.shape[1:3])
@@ -1506,9 +1522,21 @@ def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Ten
               "qkv_prep: caches [pages, kv_heads, page, dk] and [.., dv]")
         _need(page_table is not None and page_table.dtype == torch.int32, "qkv_prep: page_table int32")
         cols, page_size = page_table.shape[1], k_cache.shape[2]
+    per_head = head_norm or pairing == "half" or q_scale is not None or gate_cols not in (0, heads)
+    if per_head:
+        _need(wq is None and wk is None, "qkv_prep: the per-head form has no norm over the whole projections")
+        _need(q_scale is None or (q_scale.dtype == torch.float32 and q_scale.numel() == heads),
+              "qkv_prep: q_scale float32 [heads]")
+        _check(_lib().nnis_qkv_prep_heads(_ptr(a), _ptr(q_scale), _ptr(freq), _ptr(token_pos), _ptr(token_seq),
+                                          _ptr(page_table), cols, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                          _ptr(gate_out), n, heads, kv_heads, dk, dv, rot,
+                                          1 if pairing == "half" else 0, 1 if head_norm else 0, gate_cols,
+                                          page_size, ctypes.c_float(eps), code_of(q_out.dtype), _stream()),
+               "qkv_prep_heads")
+        return
     _check(_lib().nnis_qkv_prep(_ptr(a), _ptr(wq), _ptr(wk), _ptr(freq), _ptr(token_pos), _ptr(token_seq),
                                 _ptr(page_table), cols, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(gate_out),
-                                n, heads, kv_heads, dk, dv, rot, 1 if gated else 0, page_size, ctypes.c_float(eps),
+                                n, heads, kv_heads, dk, dv, rot, 1 if gate_cols else 0, page_size, ctypes.c_float(eps),
                                 code_of(q_out.dtype), _stream()), "qkv_prep")
 
 
@@ -1530,14 +1558,16 @@ def attention_sink(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     _need(pages * nkv * page_size < 2 ** 31, "attention_sink: the cache has too many rows")
     _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads), "attention_sink: sink [heads]")
     _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= n * heads), "attention_sink: gate")
+    # a gate per (token, head), or, as a matrix [n, heads * dv], per output value
+    gate_elems = dv if gate is not None and gate.dim() == 2 and gate.shape[1] == heads * dv and dv > 1 else 0
     if n_splits > 1:
         _need(partial is not None and partial.dtype == torch.float32
               and partial.numel() >= n * heads * n_splits * (dv + 2), "attention_sink: partial scratch")
     _check(_lib().nnis_attention_sink(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
                                       _ptr(page_table), page_table.shape[1], _ptr(sink), _ptr(gate), _ptr(out),
                                       _ptr(partial), n, heads, kv_heads, dk, dv, page_size, window, chunk,
-                                      ctypes.c_float(scale), ctypes.c_float(cap), n_splits, code_of(out.dtype),
-                                      _stream()), "attention_sink", 2 if n_splits > 1 else 1)
+                                      ctypes.c_float(scale), ctypes.c_float(cap), n_splits, gate_elems,
+                                      code_of(out.dtype), _stream()), "attention_sink", 2 if n_splits > 1 else 1)
 
 
 def attention_sink_mma_takes(dk: int, dv: int, page_size: int) -> bool:
@@ -1562,11 +1592,12 @@ def attention_sink_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     _need(tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 2, "attention_sink_mma: tiles [n, 2]")
     _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads), "attention_sink_mma: sink")
     _need(gate is None or (gate.dtype == torch.float32 and gate.numel() >= n * heads), "attention_sink_mma: gate")
+    gate_elems = d if gate is not None and gate.dim() == 2 and gate.shape[1] == heads * d else 0
     _check(_lib().nnis_attention_sink_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tiles), tiles.shape[0],
                                           _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table),
                                           page_table.shape[1], _ptr(sink), _ptr(gate), _ptr(out), heads, kv_heads, d,
                                           page_size, window, chunk, ctypes.c_float(scale), ctypes.c_float(cap),
-                                          _stream()), "attention_sink_mma")
+                                          gate_elems, _stream()), "attention_sink_mma")
 
 
 def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
@@ -1637,3 +1668,91 @@ def moe_grouped_gated_tc(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tens
                                             _ptr(y), _ptr(residual), n, width, ff, experts, top,
                                             sm_count(h.device), _ptr(status_word(h.device)), PDL, _stream()),
            "moe_grouped_gated_tc", 6)
+
+
+GELU_ERF, GELU_TANH = 0, 1
+
+
+def act_rows(x: torch.Tensor, out: torch.Tensor, kind: int) -> None:
+    """out = activation(x), x float32, rounded once to out's dtype; ``GELU_ERF`` or ``GELU_TANH``."""
+    _cuda(x, out)
+    _need(x.dtype == torch.float32 and x.numel() == out.numel(), "act_rows: float32 in, as many values out")
+    _check(_lib().nnis_act_rows(_ptr(x), _ptr(out), code_of(out.dtype), ctypes.c_longlong(x.numel()), kind,
+                                _stream()), "act_rows")
+
+
+def depth_mix(hidden: torch.Tensor, history: torch.Tensor, weights: torch.Tensor, terms: int) -> None:
+    """history[terms - 1] = hidden; hidden = sum over j < terms of weights[j] * history[j].
+    hidden float32 [n, width]; history float32 [at least terms, n, width]; weights float32 [terms]."""
+    _cuda(hidden, history, weights)
+    _need(hidden.dtype == history.dtype == weights.dtype == torch.float32, "depth_mix: float32")
+    _need(history.dim() == 3 and history.shape[0] >= terms and tuple(history.shape[1:]) == tuple(hidden.shape)
+          and hidden.is_contiguous() and history.is_contiguous(), "depth_mix: history [terms, n, width]")
+    _need(weights.numel() == terms and terms >= 1, "depth_mix: a weight per term")
+    _check(_lib().nnis_depth_mix(_ptr(hidden), _ptr(history), _ptr(weights), ctypes.c_longlong(hidden.numel()),
+                                 ctypes.c_longlong(hidden.numel()), terms, _stream()), "depth_mix")
+
+
+def delta_prep(a: torch.Tensor, conv_w: torch.Tensor, tail: torch.Tensor, a_log: torch.Tensor,
+               dt_bias: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor, seq_slots: torch.Tensor,
+               seq_first_row: Optional[torch.Tensor], seq_count: Optional[torch.Tensor], qkv: torch.Tensor,
+               beta_g: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, unit_eps: float,
+               q_scale: float) -> None:
+    """What the gated delta rule's recurrence reads, from the projection's float32 rows
+    [q | k | v | gate | b | a]: q, k, v through their short causal convolutions (``conv_w``
+    [channels, taps], ``tail`` [slots, taps - 1, channels], which is moved on) and silu; q and k heads
+    made unit vectors, q times ``q_scale`` (``qkv`` float32 [n, channels]); beta = sigmoid(b) and the
+    decay exp(-exp(a_log) softplus(a + dt_bias)) (``beta_g`` float32 [n, 2 heads])."""
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    _cuda(a, conv_w, tail, a_log, dt_bias, qkv, beta_g)
+    n = qkv.shape[0]
+    channels = 2 * kv_heads * dim + heads * vdim
+    taps = conv_w.shape[1]
+    _need(a.dtype == torch.float32 and tuple(a.shape) == (n, channels + heads * vdim + 2 * heads),
+          "delta_prep: float32 rows [q | k | v | gate | b | a]")
+    _need(conv_w.dtype == tail.dtype == torch.float32 and conv_w.shape[0] == channels and conv_w.is_contiguous()
+          and tail.dim() == 3 and tuple(tail.shape[1:]) == (max(taps - 1, 1), channels),
+          "delta_prep: float32 conv_w [channels, taps], tail [slots, taps - 1, channels]")
+    _need(a_log.dtype == dt_bias.dtype == torch.float32 and a_log.numel() == dt_bias.numel() == heads,
+          "delta_prep: a_log, dt_bias float32 [heads]")
+    _need(qkv.dtype == beta_g.dtype == torch.float32 and qkv.shape[1] == channels
+          and tuple(beta_g.shape) == (n, 2 * heads), "delta_prep: qkv [n, channels], beta_g [n, 2 heads] float32")
+    units = seq_first_row.numel() if seq_first_row is not None else n
+    _check(_lib().nnis_delta_prep(_ptr(a), _ptr(conv_w), _ptr(tail), _ptr(a_log), _ptr(dt_bias), _ptr(token_pos),
+                                  _ptr(token_seq), _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(qkv),
+                                  _ptr(beta_g), n, units, heads, kv_heads, dim, vdim, taps,
+                                  ctypes.c_float(unit_eps), ctypes.c_float(q_scale), _stream()),
+           "delta_prep", 2 if taps > 1 else 1)
+
+
+def delta_scan(qkv: torch.Tensor, beta_g: torch.Tensor, state: torch.Tensor, token_pos: torch.Tensor,
+               token_seq: torch.Tensor, seq_slots: torch.Tensor, seq_first_row: Optional[torch.Tensor],
+               seq_count: Optional[torch.Tensor], o_raw: torch.Tensor, heads: int, kv_heads: int, dim: int,
+               vdim: int) -> None:
+    """The gated delta rule over the step's tokens, from and into ``state`` float32
+    [slots, heads, dim, vdim]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+    _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
+    _cuda(qkv, beta_g, state, o_raw)
+    n = qkv.shape[0]
+    _need(qkv.dtype == beta_g.dtype == state.dtype == o_raw.dtype == torch.float32, "delta_scan: float32")
+    _need(qkv.shape[1] == 2 * kv_heads * dim + heads * vdim and tuple(beta_g.shape) == (n, 2 * heads)
+          and tuple(state.shape[1:]) == (heads, dim, vdim) and o_raw.numel() >= n * heads * vdim,
+          "delta_scan: qkv [n, channels], beta_g [n, 2 heads], state [slots, heads, dim, vdim]")
+    units = seq_first_row.numel() if seq_first_row is not None else n
+    _check(_lib().nnis_delta_scan(_ptr(qkv), _ptr(beta_g), _ptr(state), _ptr(token_pos), _ptr(token_seq),
+                                  _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(o_raw), units, heads,
+                                  kv_heads, dim, vdim, _stream()), "delta_scan")
+
+
+def delta_finish(o_raw: torch.Tensor, gate_rows: torch.Tensor, gate_off: int, weight: torch.Tensor,
+                 token_pos: torch.Tensor, out: torch.Tensor, heads: int, vdim: int, eps: float) -> None:
+    """out[n, h] = o[n, h] / rms(o[n, h]) * weight * silu(gate[n, h]); the gate's logits are the
+    float32 columns ``gate_off ...`` of ``gate_rows``; ``weight`` float32 [vdim] serves every head."""
+    _cuda(o_raw, gate_rows, weight, token_pos, out)
+    n = out.shape[0]
+    _need(o_raw.dtype == gate_rows.dtype == weight.dtype == torch.float32 and weight.numel() == vdim
+          and gate_rows.dim() == 2 and gate_rows.shape[1] >= gate_off + heads * vdim
+          and tuple(out.shape) == (n, heads * vdim), "delta_finish: shapes")
+    _check(_lib().nnis_delta_finish(_ptr(o_raw), _ptr(gate_rows), gate_rows.shape[1], gate_off, _ptr(weight),
+                                    _ptr(token_pos), _ptr(out), n, heads, vdim, ctypes.c_float(eps),
+                                    code_of(out.dtype), _stream()), "delta_finish")

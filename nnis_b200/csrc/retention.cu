@@ -12,13 +12,23 @@
 //                    stands): 32 tokens at a time, see below.
 //   retention_prefix, retention_carry   long prompts cut into runs that are worked side by
 //                    side: the states between the runs, and what they give each token.
-//   retention_gate   o / rms(o) per head, times silu(g), rounded once.
+//   retention_gate   o / rms(o) per head, times silu(g) (or sigmoid(g)), rounded once;
+//   retention_gate_joined   the same with one norm over a token's joined heads and a weight per value.
+//
+// `act` passes q, k and v through silu as they are read; `k_scale` multiplies k (dim^-1/2 in
+// retention proper, 1 for a recurrence without a scale).
 //
 // Packed input rows: [q (H dim) | k (H dim) | v (H vdim) | g (H vdim)].
 #include "async_copy.cuh"
 #include "common.cuh"
 
 namespace nnis {
+
+// a projection's value as it enters the recurrence: as it is, or through silu (`act`)
+template <typename T> __device__ __forceinline__ float pre(T x, int act) {
+    const float f = to_float(x);
+    return act ? f / (1.0f + expf(-f)) : f;
+}
 
 template <typename T, int R>
 __global__ void __launch_bounds__(256)
@@ -27,7 +37,7 @@ retention_scan_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq
                       const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                       const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
                       const int* __restrict__ seq_start, const int* __restrict__ seq_count,
-                      float* __restrict__ o_raw, int heads, int dim, int vdim, int rot_dims) {
+                      float* __restrict__ o_raw, int heads, int dim, int vdim, int rot_dims, int act, float k_scale) {
     extern __shared__ float smem[];
     pdl_wait();
     pdl_launch_dependents();
@@ -51,7 +61,6 @@ retention_scan_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq
     if (count <= 0) return;
     const bool live = col < vdim;
     const float g = decay[h];
-    const float k_scale = 1.0f / sqrtf((float)dim);
     float* S = state + (((size_t)slot * heads + h) * dim) * vdim;
     float s[R];
 #pragma unroll
@@ -70,20 +79,20 @@ retention_scan_kernel(const T* __restrict__ qkvg, const float* __restrict__ freq
             if (j < half) {
                 float ang = pos * freq[j];
                 float c = cosf(ang), sn = sinf(ang);
-                float u = to_float(qh[j]), v = to_float(qh[j + half]);
+                float u = pre(qh[j], act), v = pre(qh[j + half], act);
                 qs[j] = u * c - v * sn;
                 qs[j + half] = v * c + u * sn;
-                u = to_float(kh[j]);
-                v = to_float(kh[j + half]);
+                u = pre(kh[j], act);
+                v = pre(kh[j + half], act);
                 ks[j] = (u * c - v * sn) * k_scale;
                 ks[j + half] = (v * c + u * sn) * k_scale;
             } else {
-                qs[j + half] = to_float(qh[j + half]);
-                ks[j + half] = to_float(kh[j + half]) * k_scale;
+                qs[j + half] = pre(qh[j + half], act);
+                ks[j + half] = pre(kh[j + half], act) * k_scale;
             }
         }
         __syncthreads();
-        float v = live ? to_float(row[(size_t)2 * heads * dim + (size_t)h * vdim + col]) : 0.f;
+        float v = live ? pre(row[(size_t)2 * heads * dim + (size_t)h * vdim + col], act) : 0.f;
         float o = 0.f;
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -128,7 +137,7 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
                        const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_count,
                        const int* __restrict__ segments, int seg_len, float* __restrict__ seg_state,
-                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims) {
+                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims, int act, float k_scale) {
     constexpr int C = kRetChunk, dim = 32 * DR4, ld = dim + 4, DR = 4 * DR4;
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;                  // [C][dim + 4]
@@ -150,7 +159,6 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
     if (count <= 0) return;
     const bool live = col < vdim;
     const float g = decay[h];
-    const float k_scale = 1.0f / sqrtf((float)dim);
     float* S = segments ? seg_state + (((size_t)blockIdx.x * heads + h) * dim) * vdim
                         : state + (((size_t)seq_slots[unit] * heads + h) * dim) * vdim;
     for (int d = warp; d < dim; d += 8) Ss[d * 32 + lane] = live && !segments ? S[(size_t)d * vdim + col] : 0.f;
@@ -175,24 +183,24 @@ retention_chunk_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
             if (j < half) {
                 float ang = (float)(start + t0 + i) * freq[j];
                 float c = cosf(ang), sn = sinf(ang);
-                float u = to_float(qh[j]), v = to_float(qh[j + half]);
+                float u = pre(qh[j], act), v = pre(qh[j + half], act);
                 qs[i * ld + j] = u * c - v * sn;
                 qs[i * ld + j + half] = v * c + u * sn;
-                u = to_float(kh[j]);
-                v = to_float(kh[j + half]);
+                u = pre(kh[j], act);
+                v = pre(kh[j + half], act);
                 ks[i * ld + j] = (u * c - v * sn) * k_scale;
                 ks[i * ld + j + half] = (v * c + u * sn) * k_scale;
             } else {
-                qs[i * ld + j + half] = to_float(qh[j + half]);
-                ks[i * ld + j + half] = to_float(kh[j + half]) * k_scale;
+                qs[i * ld + j + half] = pre(qh[j + half], act);
+                ks[i * ld + j + half] = pre(kh[j + half], act) * k_scale;
             }
         }
         for (int it = tid; it < C * 32; it += 256) {
             int i = it >> 5;
             float v = 0.f;
             if (i < cnt && live)
-                v = to_float(qkvg[(size_t)(first + t0 + i) * row_len + (size_t)2 * heads * dim +
-                                  (size_t)h * vdim + col]);
+                v = pre(qkvg[(size_t)(first + t0 + i) * row_len + (size_t)2 * heads * dim +
+                             (size_t)h * vdim + col], act);
             vs[it] = v;
         }
         __syncthreads();
@@ -318,7 +326,7 @@ retention_carry_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
                        const float* __restrict__ decay, const float* __restrict__ seg_state,
                        const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
                        const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
-                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims) {
+                       float* __restrict__ o_raw, int heads, int vdim, int rot_dims, int act, float k_scale) {
     constexpr int C = kRetChunk, dim = 32 * DR4, ld = dim + 4;
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;             // [C][dim + 4]
@@ -352,11 +360,11 @@ retention_carry_kernel(const T* __restrict__ qkvg, const float* __restrict__ fre
             if (j < half) {
                 float ang = (float)(start + t0 + i) * freq[j];
                 float c = cosf(ang), sn = sinf(ang);
-                float u = to_float(qh[j]), v = to_float(qh[j + half]);
+                float u = pre(qh[j], act), v = pre(qh[j + half], act);
                 qs[i * ld + j] = u * c - v * sn;
                 qs[i * ld + j + half] = v * c + u * sn;
             } else {
-                qs[i * ld + j + half] = to_float(qh[j + half]);
+                qs[i * ld + j + half] = pre(qh[j + half], act);
             }
         }
         __syncthreads();
@@ -389,7 +397,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 retention_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ qkvg,
                       const int* __restrict__ token_pos, T* __restrict__ out, long long n_units,
-                      int heads, int dim, int vdim, float eps) {
+                      int heads, int dim, int vdim, float eps, int gate_kind) {
     pdl_wait();
     pdl_launch_dependents();
     long long unit = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -411,7 +419,43 @@ retention_gate_kernel(const float* __restrict__ o_raw, const T* __restrict__ qkv
     float s = 1.0f / sqrtf(ss / (float)vdim + eps);
     for (int i = lane; i < vdim; i += 32) {
         float z = to_float(gate[i]);
-        dst[i] = from_float<T>((o[i] * s) * (z / (1.0f + expf(-z))));
+        float sg = 1.0f / (1.0f + expf(-z));
+        dst[i] = from_float<T>((o[i] * s) * (gate_kind ? sg : z * sg));
+    }
+}
+
+// The same with ONE norm over the joined heads of a token and a weight per value:
+// out[n, :] = o[n, :] / sqrt(mean(o[n, :]^2) + eps) * w * gate(g[n, :]); a CTA per token
+template <typename T>
+__global__ void __launch_bounds__(256)
+retention_gate_joined_kernel(const float* __restrict__ o_raw, const T* __restrict__ qkvg,
+                             const float* __restrict__ w, const int* __restrict__ token_pos, T* __restrict__ out,
+                             int heads, int dim, int vdim, float eps, int gate_kind) {
+    __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t n = blockIdx.x;
+    const int cols = heads * vdim;
+    T* dst = out + n * cols;
+    if (token_pos[n] < 0) {
+        for (int i = threadIdx.x; i < cols; i += 256) dst[i] = from_float<T>(0.f);
+        return;
+    }
+    const float* o = o_raw + n * cols;
+    const T* gate = qkvg + n * ((size_t)2 * heads * dim + (size_t)2 * cols) + (size_t)2 * heads * dim + cols;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < cols; i += 256) ss = fmaf(o[i], o[i], ss);
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += red[k];
+    const float s = 1.0f / sqrtf(total / (float)cols + eps);
+    for (int i = threadIdx.x; i < cols; i += 256) {
+        float z = to_float(gate[i]);
+        float sg = 1.0f / (1.0f + expf(-z));
+        dst[i] = from_float<T>((o[i] * s) * w[i] * (gate_kind ? sg : z * sg));
     }
 }
 
@@ -421,7 +465,8 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
                             const int* seq_first_row, const int* seq_start, const int* seq_count,
                             const int* segments, int n_segments, const int* seq_first_segment, int seg_len,
                             float* seg_state, float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
-                            int vdim, int rot_dims, float eps, cudaStream_t stream) {
+                            int vdim, int rot_dims, float eps, int act, float k_scale, const float* norm_w,
+                            int gate_kind, cudaStream_t stream) {
     dim3 grid(n_units, heads, (vdim + 31) / 32);
     if (seq_first_row && (dim == 32 || dim == 64 || dim == 128 || dim == 256)) {
         // a prompt step: chunks of tokens (other key sizes walk the tokens one by one below)
@@ -439,7 +484,7 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
             if (e == cudaSuccess) \
                 kernel<<<chunk_grid, 256, chunk_smem, stream>>>((const T*)qkvg, freq, decay, state, seq_slots, \
                                                                 seq_first_row, seq_start, seq_count, segments, \
-                                                                seg_len, seg_state, o_raw, heads, vdim, rot_dims); \
+                                                                seg_len, seg_state, o_raw, heads, vdim, rot_dims, act, k_scale); \
             if (e == cudaSuccess && segments) { \
                 retention_prefix_kernel<<<dim3(n_units, heads, (dim * vdim + 255) / 256), 256, 0, stream>>>( \
                     seg_state, state, decay, seq_slots, seq_count, seq_first_segment, seg_len, heads, dim * vdim); \
@@ -449,7 +494,7 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
                 if (e == cudaSuccess) \
                     carry<<<chunk_grid, 256, carry_smem, stream>>>((const T*)qkvg, freq, decay, seg_state, \
                                                                    seq_first_row, seq_start, seq_count, segments, \
-                                                                   seg_len, o_raw, heads, vdim, rot_dims); \
+                                                                   seg_len, o_raw, heads, vdim, rot_dims, act, k_scale); \
             } \
         } while (0)
         if (dim == 32) NNIS_RET_CHUNK(1);
@@ -460,9 +505,14 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
         if (e != cudaSuccess) return (int)e;
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
+        if (norm_w) {
+            retention_gate_joined_kernel<T><<<(unsigned)n_tokens, 256, 0, stream>>>(
+                o_raw, (const T*)qkvg, norm_w, token_pos, (T*)out, heads, dim, vdim, eps, gate_kind);
+            NNIS_RETURN_LAUNCH();
+        }
         long long gate_units = (long long)n_tokens * heads;
         retention_gate_kernel<T><<<(unsigned)((gate_units + 7) / 8), 256, 0, stream>>>(
-            o_raw, (const T*)qkvg, token_pos, (T*)out, gate_units, heads, dim, vdim, eps);
+            o_raw, (const T*)qkvg, token_pos, (T*)out, gate_units, heads, dim, vdim, eps, gate_kind);
         NNIS_RETURN_LAUNCH();
     }
     size_t smem = (2 * (size_t)dim + 256) * sizeof(float);
@@ -470,16 +520,23 @@ static int launch_retention(const void* qkvg, const float* freq, const float* de
 #define NNIS_RET_CASE(R) \
     le = launch_dependent(retention_scan_kernel<T, R>, grid, 256, smem, stream, (const T*)qkvg, freq, decay, state, \
                           token_pos, token_seq, seq_slots, seq_first_row, seq_start, seq_count, o_raw, heads, dim, \
-                          vdim, rot_dims)
+                          vdim, rot_dims, act, k_scale)
     if (dim <= 32) NNIS_RET_CASE(4);
     else if (dim <= 64) NNIS_RET_CASE(8);
     else if (dim <= 128) NNIS_RET_CASE(16);
     else NNIS_RET_CASE(32);
 #undef NNIS_RET_CASE
     if (le != cudaSuccess) return (int)le;
+    if (norm_w) {
+        le = launch_dependent(retention_gate_joined_kernel<T>, (unsigned)n_tokens, 256, 0, stream,
+                              (const float*)o_raw, (const T*)qkvg, norm_w, token_pos, (T*)out, heads, dim, vdim, eps,
+                              gate_kind);
+        return le == cudaSuccess ? NNIS_OK : (int)le;
+    }
     long long units = (long long)n_tokens * heads;
     le = launch_dependent(retention_gate_kernel<T>, (unsigned)((units + 7) / 8), 256, 0, stream,
-                          (const float*)o_raw, (const T*)qkvg, token_pos, (T*)out, units, heads, dim, vdim, eps);
+                          (const float*)o_raw, (const T*)qkvg, token_pos, (T*)out, units, heads, dim, vdim, eps,
+                          gate_kind);
     return le == cudaSuccess ? NNIS_OK : (int)le;
 }
 
@@ -494,12 +551,15 @@ using namespace nnis;
 // the run among the sequence's tokens of this step), runs of `seg_len` tokens in the order
 // of the sequences, with `seq_first_segment` [n_units + 1] and `seg_state` float32
 // [n_segments, heads, dim, vdim]: the runs are worked side by side.
+// `act` 1: q, k, v through silu; `k_scale`: the keys' multiplier; `norm_w` (float32 [heads * vdim]): one
+// norm over the joined heads with this weight instead of a norm per head; `gate_kind` 0 silu, 1 sigmoid.
 NNIS_API int nnis_retention(const void* qkvg, const float* freq, const float* decay, float* state,
                             const int* token_pos, const int* token_seq, const int* seq_slots,
                             const int* seq_first_row, const int* seq_start, const int* seq_count,
                             const int* segments, int n_segments, const int* seq_first_segment, int seg_len,
                             float* seg_state, float* o_raw, void* out, int n_tokens, int n_units, int heads, int dim,
-                            int vdim, int rot_dims, float eps, int dtype, cudaStream_t stream) {
+                            int vdim, int rot_dims, float eps, int act, float k_scale, const float* norm_w,
+                            int gate_kind, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || n_units <= 0 || heads <= 0 || dim <= 0 || vdim <= 0 || rot_dims < 0 ||
         (rot_dims & 1) || rot_dims > dim || !(eps > 0.f) || !qkvg || !freq || !decay || !state ||
         !token_pos || !token_seq || !seq_slots || !o_raw || !out)
@@ -514,11 +574,11 @@ NNIS_API int nnis_retention(const void* qkvg, const float* freq, const float* de
         return launch_retention<float>(qkvg, freq, decay, state, token_pos, token_seq, seq_slots,
                                        seq_first_row, seq_start, seq_count, segments, n_segments,
                                        seq_first_segment, seg_len, seg_state, o_raw, out, n_tokens,
-                                       n_units, heads, dim, vdim, rot_dims, eps, stream);
+                                       n_units, heads, dim, vdim, rot_dims, eps, act, k_scale, norm_w, gate_kind, stream);
     if (dtype == NNIS_DTYPE_BF16)
         return launch_retention<bf16>(qkvg, freq, decay, state, token_pos, token_seq, seq_slots,
                                       seq_first_row, seq_start, seq_count, segments, n_segments,
                                       seq_first_segment, seg_len, seg_state, o_raw, out, n_tokens,
-                                      n_units, heads, dim, vdim, rot_dims, eps, stream);
+                                      n_units, heads, dim, vdim, rot_dims, eps, act, k_scale, norm_w, gate_kind, stream);
     return NNIS_ERR_UNSUPPORTED;
 }

@@ -1,5 +1,5 @@
-from . import (attention, block, embedding, latent_attention, mlp, moe, norm, position,  # noqa: F401
-               retention, selective_scan, sink_attention, wkv)  # (registration)
+from . import (attention, block, delta_rule, embedding, latent_attention, mixer_pair, mlp, moe,  # noqa: F401
+               norm, position, retention, selective_scan, sink_attention, wkv)  # (registration)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Part,
                    PositionEncoding, Registry)
 from .block import Block

@@ -12,6 +12,11 @@ class registered in ``BLOCKS``, not a change here.
 stream itself and the norm stands on their OUTPUT; roles mixer, mixer_norm, and optionally
 ffn, ffn_norm; ``LayerSpec.params["residual_mult"]`` is m.
 
+``sandwich``: h += norm1b(mixer(norm1(h))); h += norm2b(ffn(norm2(h))): a norm before and a norm
+after every sub-layer; roles mixer_norm, mixer, mixer_post_norm and, optionally, ffn_norm, ffn,
+ffn_post_norm.  With ``LayerSpec.params["depth_mix"]`` the block's result is kept beside the
+results of the blocks before it, and what goes on is a learned weighted sum of them all.
+
 ``prenorm``: h += mixer(norm1(h)); h += ffn(norm2(h)) - the order of NNIS's
 decoder (crates/nnis-model/src/runtime.rs:946-1097); roles mixer_norm, mixer,
 ffn_norm, ffn.  In decode steps a norm may be shared out between the projections on
@@ -250,6 +255,79 @@ class BranchNormBlock(Block):
         ctx.hidden_copy = x if self.dtype != torch.float32 else None
 
 
+class SandwichBlock(Block):
+    """A norm before and a norm after each sub-layer: x += norm1b(mixer(norm1(x))), then
+    x += norm2b(ffn(norm2(x))).  The sub-layer adds its output up in a zeroed float32 branch buffer,
+    as it would into the residual stream, and one kernel norms that buffer and adds it to the stream
+    (leaving the buffer zero again).  Roles: mixer_norm, mixer, mixer_post_norm and, optionally, ffn_norm,
+    ffn, ffn_post_norm; the norms after the sub-layers are RMS norms (``rmsnorm``).
+
+    ``LayerSpec.params["depth_mix"]`` = {"name": tensor stem, "terms": t, "most": m} turns on the depth-weighted
+    average: with X_0 what the first such block of a run was given and X_t-1 this block's result, the
+    stream that goes on is sum_j w[j] X_j over the t results so far (w: the block's tensor of t
+    weights).  The results live in the step's workspace, one float32 copy of the stream each (room for m,
+    the most terms of any block of the model, so that the buffer never moves inside a run); the first
+    block of a run (``terms == 2``) keeps its own input as X_0."""
+
+    def __init__(self, layer_spec, dtype: torch.dtype, device: torch.device):
+        super().__init__(layer_spec, dtype, device)
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.mixer_post = self.build(NORMS, "mixer_post_norm")
+        self.ffn = self.build(FEED_FORWARDS, "ffn") if "ffn" in layer_spec.parts else None
+        self.ffn_norm = self.build(NORMS, "ffn_norm") if self.ffn is not None else None
+        self.ffn_post = self.build(NORMS, "ffn_post_norm") if self.ffn is not None else None
+        for norm in (self.mixer_post, self.ffn_post):
+            if norm is not None and getattr(norm, "kind", None) != "rmsnorm":
+                raise ValueError("sandwich: the norm on a sub-layer's output is an rmsnorm")
+        mix = layer_spec.params.get("depth_mix")
+        self.mix_terms = int(mix["terms"]) if mix else 0
+        self.mix_most = max(int(mix.get("most", 0)), self.mix_terms) if mix else 0
+        self.mix_name = f"{layer_spec.prefix}.{mix['name']}" if mix else None
+        if mix and self.mix_terms < 2:
+            raise ValueError("sandwich: a depth mix has at least two terms (the input and this block's result)")
+        self.mix_weights = None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn,
+                                 self.ffn_post) if p is not None)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        if self.mix_name:
+            specs[self.mix_name] = WeightSpec((self.mix_terms,), "vector", init="ones")
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        if self.mix_name:
+            self.mix_weights = tensors[self.mix_name]
+
+    def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
+        n, width = hidden.shape
+        ws = ctx.workspace
+        ctx.emit_for = None  # a norm of the branch follows every sub-layer: none may begin the next one
+        history = None
+        if self.mix_terms:
+            history = ws.get("depth_history", (self.mix_most, n, width), torch.float32)
+            if self.mix_terms == 2:
+                ops.copy_async(history[0], hidden)
+        normed = ws.get("normed_sandwich", (n, width), self.dtype)
+        branch = ws.kept_zero("branch_out", (n, width), torch.float32)
+        if not ctx.decode:
+            branch.zero_()
+        self.mixer_norm.forward(hidden, normed)
+        self.mixer.forward(normed, ctx, branch, cache)
+        ops.norm_scale_add(branch, self.mixer_post.weight, self.mixer_post.eps, 1.0, hidden, clear=True)
+        if self.ffn is not None:
+            self.ffn_norm.forward(hidden, normed)
+            self.ffn.forward(normed, ctx, branch)
+            ops.norm_scale_add(branch, self.ffn_post.weight, self.ffn_post.eps, 1.0, hidden, clear=True)
+        if history is not None:
+            ops.depth_mix(hidden, history, self.mix_weights, self.mix_terms)
+
+
 BLOCKS.register("prenorm", PreNormBlock)
+BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("branch_norm", BranchNormBlock)
 BLOCKS.register("parallel", ParallelBlock)

@@ -129,4 +129,48 @@ class GatedMLP(Part):
             linear(act, self.w_down, self.b_down, residual, ADD_F32, ws)
 
 
+class DenseMLP(Part):
+    """Feed-forward without a gate: down(act(up(x))), added to the residual.  The first product
+    leaves float32; the activation kernel rounds once to the operand dtype.
+
+    params: hidden_size, intermediate_size, activation ("gelu": 0.5 z (1 + erf(z / sqrt 2));
+    "gelu_tanh": 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), names {up, down}."""
+    ACTIVATIONS = {"gelu": ops.GELU_ERF, "gelu_tanh": ops.GELU_TANH}
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.names = params["names"]
+        self.activation = params.get("activation", "gelu")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"mlp: activation {self.activation!r} has no kernel ({sorted(self.ACTIVATIONS)})")
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        H, I = self.hidden, self.inter
+        return {self.tensor_name(self.names["up"]): WeightSpec((I, H), "matrix", fan_in=H),
+                self.tensor_name(self.names["down"]): WeightSpec((H, I), "matrix", fan_in=I)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up = tensors[self.tensor_name(self.names["up"])]
+        self.w_down = tensors[self.tensor_name(self.names["down"])]
+
+    def parameter_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def step_flops(self, counts, starts) -> float:
+        return 2.0 * 2 * self.hidden * self.inter * sum(counts)
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        n = residual.shape[0]
+        ws = ctx.workspace
+        up = ws.get("mlp_up", (n, self.inter), torch.float32)
+        linear(x, self.w_up, None, up, STORE_F32, decode=ctx.decode)
+        act = ws.get("act", (n, self.inter), self.dtype)
+        ops.act_rows(up, act, self.ACTIVATIONS[self.activation])
+        linear(act, self.w_down, None, residual, ADD_F32, ws, decode=ctx.decode)
+
+
 FEED_FORWARDS.register("gated_mlp", GatedMLP)
+FEED_FORWARDS.register("mlp", DenseMLP)

@@ -17,8 +17,14 @@ cut into runs of 256 tokens that start from zero side by side, after which the s
 between the runs are put together in order and every token receives what the tokens
 before its run contribute.
 
+Variants, each a parameter: ``activation`` "silu" passes q, k and v through silu before the
+recurrence (lightning attention's form); ``key_scale`` replaces dim^-1/2 (1.0: no scale);
+``norm`` "joined" divides a token's joined heads by ONE root mean square and multiplies by a
+weight per value (names["norm"]) instead of a norm per head; ``gate`` "sigmoid" multiplies by
+sigmoid(W_g h) instead of silu(W_g h).  A position encoding of zero ``dims`` rotates nothing.
+
 params: hidden_size, heads, dim, vdim, decay (one per head), eps, position (a
-``rope_frequencies`` PartSpec), names {q, k, v, g, o}.
+``rope_frequencies`` PartSpec), activation, key_scale, norm, gate, names {q, k, v, g, o, norm}.
 """
 from __future__ import annotations
 
@@ -53,7 +59,15 @@ class Retention(Part):
             raise ValueError("retention rotates by a table of frequencies (rope_frequencies)")
         if self.position.dims > self.dim:
             raise ValueError(f"rotation over {self.position.dims} dimensions of heads of {self.dim}")
-        self.w_in = self.w_o = None
+        self.activation = params.get("activation") or "none"
+        self.key_scale = params.get("key_scale")
+        self.norm = params.get("norm", "head")
+        self.gate = params.get("gate", "silu")
+        if self.activation not in ("none", "silu") or self.norm not in ("head", "joined") \
+                or self.gate not in ("silu", "sigmoid"):
+            raise ValueError(f"retention: activation {self.activation!r}, norm {self.norm!r} or gate "
+                             f"{self.gate!r} is not known")
+        self.w_in = self.w_o = self.norm_weight = None
         self._decay = None
 
     def _name(self, key: str) -> str:
@@ -61,16 +75,21 @@ class Retention(Part):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         W, H = self.hidden, self.heads
-        return {self._name("q"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
-                self._name("k"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
-                self._name("v"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
-                self._name("g"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
-                self._name("o"): WeightSpec((W, H * self.vdim), "matrix", fan_in=H * self.vdim)}
+        specs = {self._name("q"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
+                 self._name("k"): WeightSpec((H * self.dim, W), "matrix", fan_in=W),
+                 self._name("v"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
+                 self._name("g"): WeightSpec((H * self.vdim, W), "matrix", fan_in=W),
+                 self._name("o"): WeightSpec((W, H * self.vdim), "matrix", fan_in=H * self.vdim)}
+        if self.norm == "joined":
+            specs[self._name("norm")] = WeightSpec((H * self.vdim,), "vector", init="ones")
+        return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.w_in = torch.cat([tensors[self._name(p)] for p in ("q", "k", "v", "g")], 0).contiguous()
         self.w_o = tensors[self._name("o")]
         self._decay = torch.tensor(self.decay_values, dtype=torch.float32, device=self.w_o.device)
+        if self.norm == "joined":
+            self.norm_weight = tensors[self._name("norm")]
 
     def parameter_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
@@ -111,7 +130,10 @@ class Retention(Part):
                       ctx.token_seq, ctx.seq_slots, ctx.seq_first_row, ctx.seq_start, ctx.seq_count,
                       o_raw, gated, H, self.dim, self.vdim, self.position.dims, self.eps,
                       segments=segments, seq_first_segment=ctx.tables.get(self.FIRST_SEGMENT),
-                      seg_state=seg_state, seg_len=ops.RETENTION_SEGMENT)
+                      seg_state=seg_state, seg_len=ops.RETENTION_SEGMENT,
+                      activation=self.activation == "silu",
+                      key_scale=None if self.key_scale is None else float(self.key_scale),
+                      norm_weight=self.norm_weight, gate=self.gate)
         linear(gated, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 

@@ -4,17 +4,23 @@ carries one more term, whose scores are capped, and whose heads are gated.
 With h the part's input, H query heads of ``dim`` values, G key/value heads (query head
 i reads key/value head i // (H / G)) with values of ``vdim``:
 
-* q = W_q h, k = W_k h, v = W_v h, no biases.  With ``qk_norm`` q and k are divided by
+* q = W_q h, k = W_k h, v = W_v h, no biases.  With ``qk_norm`` (True) q and k are divided by
   their root mean square taken over the WHOLE projection (all heads at once) and
-  multiplied by a weight per column, before the rotation.
+  multiplied by a weight per column, before the rotation.  With ``qk_norm == "head"`` every
+  head of q and of k is divided by its own root mean square AFTER the rotation, without a weight.
 * q and k are rotated by position over the first ``dims`` values of every head (the
-  position encoding's frequencies; neighbouring pairs).
+  position encoding's frequencies; neighbouring pairs, or, for an encoding whose ``pairing`` is
+  "half", value i with value i + dims / 2).
+* With ``head_scale`` the scores of head i are also multiplied by a learned number per head
+  (names["head_scale"]: a temperature); it is folded into q.
 * score = cap * tanh(scale * q.k / cap) (``softcap`` 0: no cap); a query at position p sees
   keys j <= p of its own chunk (``chunk`` > 0: floor(j / chunk) == floor(p / chunk), chunks
   counted from position 0 of the sequence) and window (``window`` > 0: j > p - window).
 * With ``sink`` the softmax's denominator also holds exp(sink_i), a learned number per
   head with no key and no value.
-* With ``gate`` head i's output is multiplied by sigmoid(W_g h)_i before W_o.
+* With ``gate`` (True or "head") head i's output is multiplied by sigmoid(W_g h)_i before W_o; with
+  ``gate == "value"`` W_g has a row per output value and the joined heads are multiplied value by
+  value by sigmoid(W_g h).
 
 Keys (after norm and rotation) and values live in the cache; with ``kv == "shared"`` the
 part has no k/v projection, norm or cache of its own and reads another schedule entry's.
@@ -24,8 +30,8 @@ kernel serves prompts, later portions and single tokens alike; prompt steps in b
 key and value heads of 64 or 128 run a tensor-core form of it (``attention_sink_mma``).
 
 params: hidden_size, heads, kv_heads, dim, vdim, scale, softcap, chunk, window, sink,
-gate, qk_norm, eps, position (a ``rope_frequencies`` PartSpec with neighbouring pairs),
-kv ("own" | "shared"), names {q, k, v, o, q_norm, k_norm, sink, gate}.
+gate, qk_norm, head_scale, eps, position (a ``rope_frequencies`` PartSpec),
+kv ("own" | "shared"), names {q, k, v, o, q_norm, k_norm, sink, gate, head_scale}.
 """
 from __future__ import annotations
 
@@ -54,8 +60,17 @@ class SinkAttention(Part):
         self.chunk = int(params.get("chunk") or 0)
         self.window = int(params.get("window") or 0)
         self.has_sink = bool(params.get("sink", False))
-        self.has_gate = bool(params.get("gate", False))
-        self.qk_norm = bool(params.get("qk_norm", False))
+        gate = params.get("gate", False)
+        if gate not in (False, True, None, "head", "value"):
+            raise ValueError(f"sink attention: gate {gate!r} is not known (head, value)")
+        self.has_gate = bool(gate)
+        self.gate_by_value = gate == "value"
+        norm = params.get("qk_norm", False)
+        if norm not in (False, True, None, "whole", "head"):
+            raise ValueError(f"sink attention: qk_norm {norm!r} is not known (whole, head)")
+        self.head_norm = norm == "head"
+        self.qk_norm = bool(norm) and not self.head_norm
+        self.has_head_scale = bool(params.get("head_scale", False))
         self.eps = float(params.get("eps", 1e-6))
         self.own_kv = params.get("kv", "own") == "own"
         self.names = params["names"]
@@ -66,12 +81,16 @@ class SinkAttention(Part):
                              f"got {self.dim}, {self.vdim}")
         pos = params["position"]
         self.position = POSITIONS.build(pos.kind, pos.params, prefix, dtype, device)
-        if not hasattr(self.position, "frequencies") or getattr(self.position, "pairing", None) != "neighbours":
-            raise ValueError("sink attention rotates neighbouring pairs by a table of frequencies")
+        if not hasattr(self.position, "frequencies"):
+            raise ValueError("sink attention rotates by a table of frequencies")
+        self.pairing = getattr(self.position, "pairing", "neighbours")
+        if self.qk_norm and self.pairing != "neighbours":
+            raise ValueError("sink attention: the norm over whole projections goes with neighbouring pairs")
         if self.position.dims > self.dim:
             raise ValueError(f"rotation over {self.position.dims} values of heads of {self.dim}")
         self.stored_kv = self.kv_heads if self.own_kv else 0
-        self.w_in = self.w_o = self.q_norm = self.k_norm = self.sink = None
+        self.gate_cols = (self.heads * self.vdim if self.gate_by_value else self.heads) if self.has_gate else 0
+        self.w_in = self.w_o = self.q_norm = self.k_norm = self.sink = self.head_scale = None
 
     def _name(self, key: str) -> str:
         return self.tensor_name(self.names[key])
@@ -81,7 +100,7 @@ class SinkAttention(Part):
         if self.own_kv:
             rows += [("k", self.kv_heads * self.dim), ("v", self.kv_heads * self.vdim)]
         if self.has_gate:
-            rows.append(("gate", self.heads))
+            rows.append(("gate", self.gate_cols))
         return rows
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -94,6 +113,8 @@ class SinkAttention(Part):
                 specs[self._name("k_norm")] = WeightSpec((self.kv_heads * self.dim,), "vector", init="ones")
         if self.has_sink:
             specs[self._name("sink")] = WeightSpec((self.heads,), "vector")
+        if self.has_head_scale:
+            specs[self._name("head_scale")] = WeightSpec((self.heads,), "vector", init="ones")
         return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -104,6 +125,8 @@ class SinkAttention(Part):
             self.k_norm = tensors[self._name("k_norm")] if self.own_kv else None
         if self.has_sink:
             self.sink = tensors[self._name("sink")]
+        if self.has_head_scale:
+            self.head_scale = tensors[self._name("head_scale")]
 
     def parameter_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
@@ -154,10 +177,11 @@ class SinkAttention(Part):
         rows = ws.get("sink_attention_in", (n, self.w_in.shape[0]), torch.float32)
         linear(x, self.w_in, None, rows, STORE_F32, decode=ctx.decode)
         q = ws.get("sink_attention_q", (n, H * self.dim), self.dtype)
-        gate = ws.get("sink_attention_gate", (n, H), torch.float32) if self.has_gate else None
+        gate = ws.get("sink_attention_gate", (n, self.gate_cols), torch.float32) if self.has_gate else None
         ops.qkv_prep(rows, self.q_norm, self.k_norm, self.position.frequencies(), ctx.token_pos, ctx.token_seq,
                      table if G else None, q, cache.k if G else None, cache.v if G else None, gate, H, G,
-                     self.dim, self.vdim, self.position.dims, self.eps)
+                     self.dim, self.vdim, self.position.dims, self.eps, pairing=self.pairing,
+                     head_norm=self.head_norm, q_scale=self.head_scale)
         out = ws.get("sink_attention_out", (n, H * self.vdim), self.dtype)
         if not ctx.decode and self._mma_prompt() and self.TILES_64 in ctx.tables:
             ops.attention_sink_mma(q, cache.k, cache.v, ctx.tables[self.TILES_64], ctx.seq_first_row, ctx.seq_start,
