@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 135m|360m|1.7b] [--batch B] [--context C] [--layers L] [--skip-points]
-                    [--skip-e2e] [--designs s,m [--only-design llama,nafezen,tazadra]]
+                    [--skip-e2e] [--designs s,m [--only-design llama,nafezen,tazadra,sedopel]]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -236,14 +236,16 @@ def timeline(engine, batch, path, rng, vocab):
 
 
 # ---------------------------------------------------------------------------
-# --designs: the Nafezen and Tazadra designs beside the Llama decoder at equal width and depth
+# --designs: the Nafezen, Tazadra and Sedopel designs beside the Llama decoder at equal width and depth
 # ---------------------------------------------------------------------------
 def design_configs(size: str):
-    """(Llama, Nafezen, Tazadra) configurations of one width, depth, vocabulary and dense
+    """(Llama, Nafezen, Tazadra, Sedopel) configurations of one width, depth, vocabulary and dense
     feed-forward size; the Nafezen layers alternate latent attention with dense and expert
     feed-forwards and hold one retention layer in four; the Tazadra layers are attention with a
     sink + dense, WKV + experts, selective scan + experts, and attention that reads the first
-    layer's keys + dense, twice."""
+    layer's keys + dense, twice; the Sedopel layers alternate a pair of mixers (gated softmax
+    attention beside lightning attention) + dense with the gated delta rule, which has a dense
+    feed-forward every other time."""
     width, heads, ff, layers, q_rank, kv_rank, experts, top = {
         "s": (1024, 16, 2816, 8, 384, 256, 16, 2),
         "m": (2048, 16, 5632, 8, 768, 512, 32, 4),
@@ -281,10 +283,21 @@ def design_configs(size: str):
         t_layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
     tazadra = {"architecture": "Tazadra", "vocab": 32768, "width": width, "norm": {"eps": 1e-5},
                "residual_mult": 0.7, "logit_softcap": 40.0, "layers": t_layers}
-    return llama, nafezen, tazadra
+    softmax = {"heads": heads, "kv_heads": heads // 4, "dim": dim, "vdim": dim, "scale": 4.0 / dim,
+               "rot": {"base": 500000.0, "dims": dim // 2}}
+    lightning = {"heads": width // 128, "dim": 64, "vdim": 128,
+                 "decay": [1.0 - 2.0 ** (-4 - i % 5) for i in range(width // 128)]}
+    delta = {"heads": width // 64, "kv_heads": width // 128, "dim": dim, "vdim": 128, "conv": 4}
+    s_layers = []
+    for i in range(layers):
+        kind, mixer, mlp = [("parallel", {"left": softmax, "right": lightning}, dense), ("delta", delta, dense),
+                            ("parallel", {"left": softmax, "right": lightning}, dense), ("delta", delta, None)][i % 4]
+        s_layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    sedopel = {"architecture": "Sedopel", "vocab": 32768, "width": width, "norm": {"eps": 1e-6}, "layers": s_layers}
+    return llama, nafezen, tazadra, sedopel
 
 
-DESIGN_NAMES = ("llama", "nafezen", "tazadra")
+DESIGN_NAMES = ("llama", "nafezen", "tazadra", "sedopel")
 
 
 def profile_steps(args) -> int:
@@ -371,7 +384,8 @@ def compare_designs(args) -> int:
             parts, marks = {}, []
             saved = []
             for block in engine.model.blocks:
-                for part in block.parts():
+                # (the members of a pair of mixers are timed too, inside the pair's own time)
+                for part in [q for p in block.parts() for q in (p, *getattr(p, "members", ()))]:
                     kind = type(part).__name__
                     saved.append((part, part.forward))
 
@@ -469,10 +483,10 @@ def main() -> int:
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     ap.add_argument("--designs", metavar="SIZES", default=None,
-                    help="instead of the benchmark: the Nafezen and Tazadra designs beside the Llama decoder at "
+                    help="instead of the benchmark: the Nafezen, Tazadra and Sedopel designs beside the Llama decoder at "
                          "equal width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
     ap.add_argument("--only-design", metavar="NAMES", default=None,
-                    help="with --designs: only these of llama, nafezen, tazadra (commas between them)")
+                    help="with --designs: only these of llama, nafezen, tazadra, sedopel (commas between them)")
     ap.add_argument("--profile-steps", type=int, default=0,
                     help="with --designs: run this many eager prompt and decode steps of one design's first "
                          "four layers for a profiler instead of the timed comparison")

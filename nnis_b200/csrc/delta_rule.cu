@@ -9,7 +9,7 @@
 // and v (float32 [taps - 1, channels], oldest first).  Everything after the projections is
 // float32 in every dtype.
 //
-//   delta_prep     a CTA per token, from the projection's float32 row
+//   delta_prep     a CTA per (token, q or k head or 256 value channels), from the projection's float32 row
 //                  [q (G dim) | k (G dim) | v (H vdim) | gate (H vdim) | b (H) | a (H)]:
 //                  the causal convolution per channel over the last `taps` inputs (inputs from
 //                  before the step come from the state, zeros at a sequence's start) and silu;
@@ -19,9 +19,13 @@
 //   delta_scan     a CTA per (sequence, head, 32 columns of vdim) walks the step's tokens in order.
 //                  A column of S never meets another, so a column is owned by KS = 8 neighbouring
 //                  lanes that hold dim / 8 of its values each in registers.  Since
-//                  o = g S^T q + u (k . q), the three sums S^T k, S^T q and k . q are reduced
-//                  together: one round of shuffles a token.  Tokens come 16 at a time through
-//                  shared memory.
+//                  o = g S^T q + u (k . q), the sums S^T k and S^T q are reduced together, one round
+//                  of shuffles a token, and k . q is made once a token for all columns.  Tokens come
+//                  16 at a time through shared memory.
+//   runs           a long prompt is cut into runs (128 tokens) that are walked side by side from
+//                  nothing (delta_scan, pass 1, which also yields every run's transition matrix),
+//                  put together in order (delta_prefix) and finished by one product a run
+//                  (delta_apply): see the kernels.
 //   delta_finish   o / rms(o) per head (eps), times a weight per value (shared by the heads),
 //                  times silu(gate), rounded once to the operand dtype.
 //
@@ -33,53 +37,64 @@ namespace nnis {
 
 __device__ __forceinline__ float delta_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
-// conv_w [conv_cols, taps] (the last column is the current token's); tail [slots, taps - 1, conv_cols]
+// conv_w [conv_cols, taps] (the last column is the current token's); tail [slots, taps - 1, conv_cols].
+// A CTA per (`per_cta` tokens, piece): pieces 0 .. 2 G - 1 are the q heads, then the k heads (dim <= 256 channels: a thread
+// a channel, then the unit vector); the pieces after them are slabs of 256 value channels; the last piece also
+// takes beta and the decay.
 __global__ void __launch_bounds__(256)
 delta_prep_kernel(const float* __restrict__ a, const float* __restrict__ conv_w, const float* __restrict__ tail,
                   const float* __restrict__ a_log, const float* __restrict__ dt_bias,
                   const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                   const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
-                  float* __restrict__ qkv, float* __restrict__ beta_g, int H, int G, int dim, int vdim, int taps,
-                  float unit_eps, float q_scale) {
-    extern __shared__ float conv_out[];  // [2 G dim] q and k after convolution and silu
+                  float* __restrict__ qkv, float* __restrict__ beta_g, int n_tokens, int per_cta, int H, int G,
+                  int dim, int vdim, int taps, float unit_eps, float q_scale) {
+    __shared__ float red[2][8];
     pdl_wait();
     pdl_launch_dependents();
-    const int n = blockIdx.x;
-    if (token_pos[n] < 0) return;
-    const int seq = token_seq[n];
-    const int slot = seq_slots[seq];
-    const int first = seq_first_row ? seq_first_row[seq] : n;
+    const int piece = blockIdx.y;
     const int L = taps - 1;
     const int nqk = 2 * G * dim, nv = H * vdim, conv_cols = nqk + nv;
     const int row_len = conv_cols + nv + 2 * H;
-    const float* old = tail + (size_t)slot * (L > 0 ? L : 1) * conv_cols;
-    for (int c = threadIdx.x; c < conv_cols; c += 256) {
-        float acc = 0.f;
-        for (int j = 0; j < taps; ++j) {
-            const int back = L - j;  // tokens before this one
-            const float in = n - back >= first ? a[(size_t)(n - back) * row_len + c]
-                                               : old[(size_t)(L - (back - (n - first))) * conv_cols + c];
-            acc = fmaf(conv_w[(size_t)c * taps + j], in, acc);
+    const bool head = piece < 2 * G;
+    const int c = head ? piece * dim + (int)threadIdx.x : nqk + (piece - 2 * G) * 256 + (int)threadIdx.x;
+    const bool in = head ? (int)threadIdx.x < dim : c < conv_cols;
+    for (int j = 0; j < per_cta; ++j) {  // (uniform over the CTA: every thread meets the barrier below)
+        const int n = blockIdx.x * per_cta + j;
+        if (n >= n_tokens) break;
+        if (token_pos[n] < 0) continue;
+        const int seq = token_seq[n];
+        const int first = seq_first_row ? seq_first_row[seq] : n;
+        const float* old = tail + (size_t)seq_slots[seq] * (L > 0 ? L : 1) * conv_cols;
+        float y = 0.f;
+        if (in) {
+            float acc = 0.f;
+            for (int t = 0; t < taps; ++t) {
+                const int back = L - t;  // tokens before this one
+                const float x = n - back >= first ? a[(size_t)(n - back) * row_len + c]
+                                                  : old[(size_t)(L - (back - (n - first))) * conv_cols + c];
+                acc = fmaf(conv_w[(size_t)c * taps + t], x, acc);
+            }
+            y = acc / (1.0f + expf(-acc));
         }
-        const float y = acc / (1.0f + expf(-acc));
-        if (c < nqk) conv_out[c] = y;
-        else qkv[(size_t)n * conv_cols + c] = y;
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int hh = warp; hh < 2 * G; hh += 8) {  // q heads, then k heads
-        const float* src = conv_out + (size_t)hh * dim;
-        float ss = 0.f;
-        for (int i = lane; i < dim; i += 32) ss = fmaf(src[i], src[i], ss);
-        const float inv = (hh < G ? q_scale : 1.0f) / sqrtf(warp_sum(ss) + unit_eps);
-        float* dst = qkv + (size_t)n * conv_cols + (size_t)hh * dim;
-        for (int i = lane; i < dim; i += 32) dst[i] = src[i] * inv;
-    }
-    const float* row = a + (size_t)n * row_len;
-    for (int h = threadIdx.x; h < H; h += 256) {
-        beta_g[(size_t)n * 2 * H + h] = 1.0f / (1.0f + expf(-row[conv_cols + nv + h]));
-        beta_g[(size_t)n * 2 * H + H + h] =
-            expf(-expf(a_log[h]) * delta_softplus(row[conv_cols + nv + H + h] + dt_bias[h]));
+        if (head) {
+            const float ss = warp_sum(y * y);
+            if ((threadIdx.x & 31) == 0) red[j & 1][threadIdx.x >> 5] = ss;
+            __syncthreads();  // (two sets of sums in turn: the next token's writers may be ahead of this one's readers)
+            float total = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) total += red[j & 1][w];
+            if (in) qkv[(size_t)n * conv_cols + c] = y * ((piece < G ? q_scale : 1.0f) / sqrtf(total + unit_eps));
+            continue;
+        }
+        if (in) qkv[(size_t)n * conv_cols + c] = y;
+        if (piece + 1 == (int)gridDim.y) {
+            const float* row = a + (size_t)n * row_len;
+            for (int h = threadIdx.x; h < H; h += 256) {
+                beta_g[(size_t)n * 2 * H + h] = 1.0f / (1.0f + expf(-row[conv_cols + nv + h]));
+                beta_g[(size_t)n * 2 * H + H + h] =
+                    expf(-expf(a_log[h]) * delta_softplus(row[conv_cols + nv + H + h] + dt_bias[h]));
+            }
+        }
     }
 }
 
@@ -118,24 +133,68 @@ constexpr int kDeltaTile = 16;  // tokens a trip through shared memory
 constexpr int kDeltaKS = 8;     // lanes that share a column of the state
 
 // KL: state values a thread holds (dim <= 8 KL).  qkv float32 [n, 2 G dim + H vdim]; beta_g float32 [n, 2 H].
-template <int KL>
+// PASS 0: a unit is a sequence (or, without the sequences' tables, a row): its tokens of the step in order, from and
+//         into the slot's state.
+// PASS 1: a unit is a run of `seg_len` tokens (`segments`: sequence, first token), worked from nothing.  The recurrence
+//         is linear in the state, S_after = P S_before + S_run with P = prod_t g_t (I - beta_t k_t k_t^T) (later tokens
+//         to the left), and every column of the state goes through it alone.  Tiles z < ceil(vdim / 32) hold value
+//         columns: they start at zero, leave the run's own outputs in o_raw and S_run in seg_state.  The tiles after
+//         them hold `dim` columns that start as the identity and see values of zero: they end as P (seg_trans
+//         [runs, H, dim, dim]), and their read-out at token t is P_t^T q_t (q_run [n, H, dim]), with which the part
+//         of o_t that comes from before the run is (P_t^T q_t)^T S_before: a product, no second walk (delta_apply).
+// A thread's KL state values of its column: key channel of register r in the eighth `part`.  Four neighbouring
+// registers are four neighbouring channels, and the eight parts' fours lie side by side: a token's q and k come from
+// shared memory 16 bytes a load, eight lanes reading 128 bytes in a row.
+__device__ __forceinline__ int delta_channel(int r, int part) { return (r >> 2) * 32 + part * 4 + (r & 3); }
+
+// rows of `dim` values from global memory into rows of `stride` floats of shared memory: the loads of a batch are all
+// issued before the first store (shared memory may alias anything, as far as the compiler knows)
+template <typename Src>
+__device__ __forceinline__ void delta_stage(float* dst, int stride, int rows, int dim, Src src) {
+    const int total = rows * dim;
+    for (int base = 0; base < total; base += 256 * 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int it = base + u * 256 + (int)threadIdx.x;
+            v[u] = it < total ? src(it / dim, it % dim) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int it = base + u * 256 + (int)threadIdx.x;
+            if (it < total) dst[(it / dim) * stride + it % dim] = v[u];
+        }
+    }
+}
+
+template <int KL, int PASS>
 __global__ void __launch_bounds__(256)
 delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_g, float* __restrict__ state,
                   const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                   const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
-                  const int* __restrict__ seq_count, float* __restrict__ o_raw, int H, int G, int dim, int vdim) {
-    constexpr int KS = kDeltaKS, TT = kDeltaTile;
+                  const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
+                  float* __restrict__ seg_state, float* __restrict__ seg_trans, float* __restrict__ q_run,
+                  float* __restrict__ o_raw, int H, int G, int dim, int vdim) {
+    constexpr int KS = kDeltaKS, TT = kDeltaTile, DP = KL * KS;  // DP: dim rounded up, the tile's row
     extern __shared__ __align__(16) float smem[];
-    float* qs = smem;              // [TT][dim]
-    float* ks = qs + TT * dim;     // [TT][dim]
-    float* vs = ks + TT * dim;     // [TT][32]
+    float* qs = smem;              // [TT][DP], zero past dim
+    float* ks = qs + TT * DP;      // [TT][DP]
+    float* vs = ks + TT * DP;      // [TT][32]
     float* bs = vs + TT * 32;      // [TT] beta
     float* gs = bs + TT;           // [TT] decay
+    float* kqs = gs + TT;          // [TT] k . q
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int i = tid; i < 2 * TT * DP; i += 256) smem[i] = 0.f;
     pdl_wait();
     pdl_launch_dependents();
     const int unit = blockIdx.x, h = blockIdx.y;
     int first, count, slot;
-    if (seq_first_row) {
+    if (PASS == 1) {
+        const int seq = segments[2 * unit], t0 = segments[2 * unit + 1];
+        first = seq_first_row[seq] + t0;
+        count = min(seg_len, seq_count[seq] - t0);
+        slot = 0;
+    } else if (seq_first_row) {
         first = seq_first_row[unit];
         count = seq_count[unit];
         slot = seq_slots[unit];
@@ -145,69 +204,212 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
         slot = seq_slots[token_seq[unit]];
     }
     if (count <= 0) return;
-    const int tid = threadIdx.x;
     const int part = tid & (KS - 1);               // which eighth of the column
-    const int col = blockIdx.z * 32 + (tid >> 3);  // the column of the state
-    const bool live = col < vdim;
+    const int value_tiles = (vdim + 31) / 32;
+    const bool trans = PASS == 1 && (int)blockIdx.z >= value_tiles;
+    const int tile0 = (trans ? (int)blockIdx.z - value_tiles : (int)blockIdx.z) * 32;
+    const int col = tile0 + (tid >> 3);            // the column of the state
+    const int ncols = trans ? dim : vdim;
+    const bool live = col < ncols;
     const int kv = h / (H / G);
     const int cols = 2 * G * dim + H * vdim;
-    float* S = state + (((size_t)slot * H + h) * dim) * vdim;
+    float* S = PASS == 0 ? state + (((size_t)slot * H + h) * dim) * vdim
+               : trans   ? seg_trans + (((size_t)unit * H + h) * dim) * dim
+                         : seg_state + (((size_t)unit * H + h) * dim) * vdim;
     float s[KL];
 #pragma unroll
-    for (int i = 0; i < KL; ++i) {
-        const int d = i * KS + part;
-        s[i] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
+    for (int r = 0; r < KL; ++r) {
+        const int d = delta_channel(r, part);
+        if (PASS == 0) s[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
+        else s[r] = (trans && live && d == col) ? 1.f : 0.f;
     }
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int cnt = min(TT, count - t0);
-        __syncthreads();  // the tile before is read
-        for (int it = tid; it < cnt * dim; it += 256) {
-            const int i = it / dim, d = it - i * dim;
-            const float* row = qkv + (size_t)(first + t0 + i) * cols;
-            qs[it] = row[(size_t)kv * dim + d];
-            ks[it] = row[(size_t)(G + kv) * dim + d];
-        }
-        for (int it = tid; it < cnt * 32; it += 256) {
-            const int i = it >> 5, c = blockIdx.z * 32 + (it & 31);
-            vs[it] = c < vdim ? qkv[(size_t)(first + t0 + i) * cols + 2 * G * dim + (size_t)h * vdim + c] : 0.f;
-        }
+        const float* rows = qkv + (size_t)(first + t0) * cols;
+        __syncthreads();  // the tile before is read (and the tiles are zero past dim)
+        delta_stage(qs, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)kv * dim + d]; });
+        delta_stage(ks, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)(G + kv) * dim + d]; });
+        delta_stage(vs, 32, cnt, 32, [&](int i, int c) {
+            return (!trans && tile0 + c < vdim) ? rows[(size_t)i * cols + 2 * G * dim + (size_t)h * vdim + tile0 + c] : 0.f;
+        });
         if (tid < cnt) {
             bs[tid] = beta_g[(size_t)(first + t0 + tid) * 2 * H + h];
             gs[tid] = beta_g[(size_t)(first + t0 + tid) * 2 * H + H + h];
         }
         __syncthreads();
+        for (int i = warp; i < cnt; i += 8) {  // k . q is the same for every column
+            float kq = 0.f;
+            for (int d = lane; d < dim; d += 32) kq = fmaf(ks[i * DP + d], qs[i * DP + d], kq);
+            kq = warp_sum(kq);
+            if (lane == 0) kqs[i] = kq;
+        }
+        __syncthreads();
         for (int i = 0; i < cnt; ++i) {
-            const float* q = qs + i * dim;
-            const float* k = ks + i * dim;
-            float sk = 0.f, sq = 0.f, kq = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * 4);
+            const float4* k4 = reinterpret_cast<const float4*>(ks + i * DP + part * 4);
+            float sk = 0.f, sq = 0.f;
             float kr[KL];
 #pragma unroll
-            for (int r = 0; r < KL; ++r) {
-                const int d = r * KS + part;
-                const float kd = d < dim ? k[d] : 0.f, qd = d < dim ? q[d] : 0.f;
-                kr[r] = kd;
-                sk = fmaf(s[r], kd, sk);
-                sq = fmaf(s[r], qd, sq);
-                kq = fmaf(kd, qd, kq);
+            for (int r4 = 0; r4 < KL / 4; ++r4) {
+                const float4 kk = k4[r4 * 8], qq = q4[r4 * 8];
+                const float kx[4] = {kk.x, kk.y, kk.z, kk.w}, qx[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    kr[r4 * 4 + e] = kx[e];
+                    sk = fmaf(s[r4 * 4 + e], kx[e], sk);
+                    sq = fmaf(s[r4 * 4 + e], qx[e], sq);
+                }
             }
 #pragma unroll
             for (int o = KS / 2; o > 0; o >>= 1) {
                 sk += __shfl_xor_sync(0xffffffffu, sk, o);
                 sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                kq += __shfl_xor_sync(0xffffffffu, kq, o);
             }
+            // o = (g S + k u^T)^T q = g S^T q + u (k . q), with S the state before the token
             const float g = gs[i];
             const float u = bs[i] * (vs[i * 32 + (tid >> 3)] - g * sk);
 #pragma unroll
             for (int r = 0; r < KL; ++r) s[r] = fmaf(kr[r], u, g * s[r]);
-            if (part == 0 && live)
-                o_raw[((size_t)(first + t0 + i) * H + h) * vdim + col] = fmaf(u, kq, g * sq);
+            if (part == 0 && live) {
+                const float o = fmaf(u, kqs[i], g * sq);
+                if (trans) q_run[((size_t)(first + t0 + i) * H + h) * dim + col] = o;
+                else o_raw[((size_t)(first + t0 + i) * H + h) * vdim + col] = o;
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < KL; ++i) {
-        const int d = i * KS + part;
-        if (live && d < dim) S[(size_t)d * vdim + col] = s[i];
+    for (int r = 0; r < KL; ++r) {
+        const int d = delta_channel(r, part);
+        if (live && d < dim) S[(size_t)d * ncols + col] = s[r];
+    }
+}
+
+// Between the runs' own walk and the product that finishes their outputs: a CTA per (sequence, head, 32 value
+// columns) walks the sequence's runs in order with the state in registers (the scan's layout).  seg_state[run]
+// (what the run adds) becomes the state before the run; the state after it is P_run S_before + S_run, a product
+// with the run's transition taken 64 of its columns at a time through shared memory; the slot's state becomes the
+// state after the last run.
+constexpr int kDeltaPrefixCols = 64;
+
+template <int KL>
+__global__ void __launch_bounds__(256)
+delta_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots,
+                    const int* __restrict__ seq_first_segment, float* __restrict__ seg_state,
+                    const float* __restrict__ seg_trans, int H, int dim, int vdim) {
+    constexpr int KS = kDeltaKS, EC = kDeltaPrefixCols, DP = KL * KS;
+    extern __shared__ __align__(16) float smem[];
+    float* cs = smem;             // [DP][32]: the carried state's columns of this tile
+    float* ps = cs + DP * 32;     // [DP][EC + 1]: EC columns of the transition, zero past dim
+    const int tid = threadIdx.x, part = tid & (KS - 1), cg = tid >> 3;
+    for (int i = tid; i < DP * (EC + 1); i += 256) ps[i] = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int col = blockIdx.z * 32 + cg;
+    const bool live = col < vdim;
+    float* S = state + (((size_t)seq_slots[seq] * H + h) * dim) * vdim;
+    float carry[KL];
+#pragma unroll
+    for (int r = 0; r < KL; ++r) {
+        const int d = delta_channel(r, part);
+        carry[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
+    }
+    const int last = seq_first_segment[seq + 1];
+    for (int run = seq_first_segment[seq]; run < last; ++run) {
+        float* local = seg_state + (((size_t)run * H + h) * dim) * vdim;
+        const float* P = seg_trans + (((size_t)run * H + h) * dim) * dim;
+        float acc[KL];
+#pragma unroll
+        for (int r = 0; r < KL; ++r) {
+            const int d = delta_channel(r, part);
+            acc[r] = (live && d < dim) ? local[(size_t)d * vdim + col] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < KL; ++r) {
+            const int d = delta_channel(r, part);
+            if (live && d < dim) local[(size_t)d * vdim + col] = carry[r];
+            cs[d * 32 + cg] = carry[r];
+        }
+        for (int e0 = 0; e0 < dim; e0 += EC) {
+            const int en = min(EC, dim - e0);
+            __syncthreads();  // cs is whole; the chunk before is read
+            delta_stage(ps, EC + 1, dim, en, [&](int d, int ee) { return P[(size_t)d * dim + e0 + ee]; });
+            __syncthreads();
+            for (int ee = 0; ee < en; ++ee) {
+                const float c = cs[(e0 + ee) * 32 + cg];
+#pragma unroll
+                for (int r = 0; r < KL; ++r) acc[r] = fmaf(ps[delta_channel(r, part) * (EC + 1) + ee], c, acc[r]);
+            }
+        }
+        __syncthreads();  // cs is read before the next run writes it
+#pragma unroll
+        for (int r = 0; r < KL; ++r) carry[r] = acc[r];
+    }
+#pragma unroll
+    for (int r = 0; r < KL; ++r) {
+        const int d = delta_channel(r, part);
+        if (live && d < dim) S[(size_t)d * vdim + col] = carry[r];
+    }
+}
+
+// o_raw[t, h, :] += S_before(run of t)^T q_run[t, h, :]: what the tokens before a run contribute to its outputs.
+// A CTA per (run, head, 32 value columns) holds its tile of S_before in registers (the scan's layout); the sums of
+// 16 tokens go through shared memory so that a row's 32 values are added to o_raw side by side.
+template <int KL>
+__global__ void __launch_bounds__(256)
+delta_apply_kernel(const float* __restrict__ q_run, const float* __restrict__ seg_state,
+                   const int* __restrict__ seq_first_row, const int* __restrict__ seq_count,
+                   const int* __restrict__ segments, int seg_len, float* __restrict__ o_raw, int H, int dim,
+                   int vdim) {
+    constexpr int KS = kDeltaKS, TT = kDeltaTile, DP = KL * KS;
+    extern __shared__ __align__(16) float smem[];
+    float* qs = smem;            // [TT][DP], zero past dim
+    float* os = qs + TT * DP;    // [TT][32]
+    const int tid = threadIdx.x, part = tid & (KS - 1);
+    for (int i = tid; i < TT * DP; i += 256) qs[i] = 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int unit = blockIdx.x, h = blockIdx.y;
+    const int seq = segments[2 * unit], t_first = segments[2 * unit + 1];
+    const int first = seq_first_row[seq] + t_first;
+    const int count = min(seg_len, seq_count[seq] - t_first);
+    if (count <= 0) return;
+    const int tile0 = blockIdx.z * 32;
+    const int col = tile0 + (tid >> 3);
+    const bool live = col < vdim;
+    const float* S = seg_state + (((size_t)unit * H + h) * dim) * vdim;
+    float s[KL];
+#pragma unroll
+    for (int r = 0; r < KL; ++r) {
+        const int d = delta_channel(r, part);
+        s[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
+    }
+    for (int t0 = 0; t0 < count; t0 += TT) {
+        const int cnt = min(TT, count - t0);
+        __syncthreads();
+        delta_stage(qs, DP, cnt, dim, [&](int i, int d) { return q_run[((size_t)(first + t0 + i) * H + h) * dim + d]; });
+        __syncthreads();
+#pragma unroll 4
+        for (int i = 0; i < cnt; ++i) {
+            const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * 4);
+            float acc = 0.f;
+#pragma unroll
+            for (int r4 = 0; r4 < KL / 4; ++r4) {
+                const float4 qq = q4[r4 * 8];
+                acc = fmaf(s[r4 * 4], qq.x, acc);
+                acc = fmaf(s[r4 * 4 + 1], qq.y, acc);
+                acc = fmaf(s[r4 * 4 + 2], qq.z, acc);
+                acc = fmaf(s[r4 * 4 + 3], qq.w, acc);
+            }
+#pragma unroll
+            for (int o = KS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (part == 0) os[i * 32 + (tid >> 3)] = acc;
+        }
+        __syncthreads();
+        for (int it = tid; it < cnt * 32; it += 256) {
+            const int i = it >> 5, c = tile0 + (it & 31);
+            if (c < vdim) o_raw[((size_t)(first + t0 + i) * H + h) * vdim + c] += os[it];
+        }
     }
 }
 
@@ -259,11 +461,13 @@ NNIS_API int nnis_delta_prep(const float* a, const float* conv_w, float* tail, c
         !seq_slots || !qkv || !beta_g)
         return NNIS_ERR_ARGUMENT;
     if (seq_first_row && !seq_count) return NNIS_ERR_ARGUMENT;
-    const size_t smem = (size_t)2 * G * dim * sizeof(float);
-    if (smem > 48 * 1024 || taps > 64) return NNIS_ERR_UNSUPPORTED;
-    cudaError_t e = launch_dependent(delta_prep_kernel, (unsigned)n_tokens, 256, smem, stream, a, conv_w,
+    if (dim > 256 || taps > 64 || 2 * G + (H * vdim + 255) / 256 > 65535) return NNIS_ERR_UNSUPPORTED;
+    const int per_cta = n_tokens > 256 ? 8 : 1;  // prompt steps: fewer, longer CTAs
+    const dim3 pieces((n_tokens + per_cta - 1) / per_cta, 2 * G + (H * vdim + 255) / 256);
+    cudaError_t e = launch_dependent(delta_prep_kernel, pieces, 256, 0, stream, a, conv_w,
                                      (const float*)tail, a_log, dt_bias, token_pos, token_seq, seq_slots,
-                                     seq_first_row, qkv, beta_g, H, G, dim, vdim, taps, unit_eps, q_scale);
+                                     seq_first_row, qkv, beta_g, n_tokens, per_cta, H, G, dim, vdim, taps, unit_eps,
+                                     q_scale);
     if (e != cudaSuccess) return (int)e;
     if (taps > 1) {
         const int conv_cols = 2 * G * dim + H * vdim;
@@ -274,22 +478,65 @@ NNIS_API int nnis_delta_prep(const float* a, const float* conv_w, float* tail, c
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
-// state float32 [slots, H, dim, vdim]; o_raw float32 [n, H vdim]
+namespace nnis {
+
+template <int KL>
+static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* state, const int* token_pos,
+                                const int* token_seq, const int* seq_slots, const int* seq_first_row,
+                                const int* seq_count, const int* segments, int n_segments,
+                                const int* seq_first_segment, int seg_len, float* seg_state, float* seg_trans,
+                                float* q_run, float* o_raw, int n_units, int H, int G, int dim, int vdim,
+                                cudaStream_t stream) {
+    const int value_tiles = (vdim + 31) / 32;
+    const size_t smem = ((size_t)2 * kDeltaTile * KL * kDeltaKS + kDeltaTile * 32 + 3 * kDeltaTile) * sizeof(float);
+    if (!segments)
+        return launch_dependent(delta_scan_kernel<KL, 0>, dim3(n_units, H, value_tiles), 256, smem, stream, qkv,
+                                beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments,
+                                seg_len, seg_state, seg_trans, q_run, o_raw, H, G, dim, vdim);
+    cudaError_t e = launch_dependent(delta_scan_kernel<KL, 1>, dim3(n_segments, H, value_tiles + (dim + 31) / 32),
+                                     256, smem, stream, qkv, beta_g, state, token_pos, token_seq, seq_slots,
+                                     seq_first_row, seq_count, segments, seg_len, seg_state, seg_trans, q_run, o_raw,
+                                     H, G, dim, vdim);
+    if (e != cudaSuccess) return e;
+    const size_t prefix_smem = (size_t)KL * kDeltaKS * (32 + kDeltaPrefixCols + 1) * sizeof(float);
+    if (prefix_smem > 48 * 1024) {
+        e = cudaFuncSetAttribute(delta_prefix_kernel<KL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)prefix_smem);
+        if (e != cudaSuccess) return e;
+    }
+    e = launch_dependent(delta_prefix_kernel<KL>, dim3(n_units, H, value_tiles), 256, prefix_smem, stream, state,
+                         seq_slots, seq_first_segment, seg_state, (const float*)seg_trans, H, dim, vdim);
+    if (e != cudaSuccess) return e;
+    return launch_dependent(delta_apply_kernel<KL>, dim3(n_segments, H, value_tiles), 256,
+                            (size_t)kDeltaTile * (KL * kDeltaKS + 32) * sizeof(float), stream, (const float*)q_run,
+                            (const float*)seg_state, seq_first_row, seq_count, segments, seg_len, o_raw, H, dim, vdim);
+}
+
+}  // namespace nnis
+
+// state float32 [slots, H, dim, vdim]; o_raw float32 [n, H vdim].  `units`: sequences of the step (with
+// seq_first_row) or rows.  With `segments` (int32 [n_segments, 2] = (sequence, first token of the run), runs of
+// seg_len tokens), seq_first_segment [sequences + 1] and scratch seg_state float32 [n_segments, H, dim, vdim],
+// seg_trans float32 [n_segments, H, dim, dim] and q_run float32 [n, H, dim] the runs are worked side by side.
 NNIS_API int nnis_delta_scan(const float* qkv, const float* beta_g, float* state, const int* token_pos,
                              const int* token_seq, const int* seq_slots, const int* seq_first_row,
-                             const int* seq_count, float* o_raw, int n_units, int H, int G, int dim, int vdim,
+                             const int* seq_count, const int* segments, int n_segments,
+                             const int* seq_first_segment, int seg_len, float* seg_state, float* seg_trans,
+                             float* q_run, float* o_raw, int n_units, int H, int G, int dim, int vdim,
                              cudaStream_t stream) {
     if (n_units <= 0 || H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || !qkv || !beta_g || !state ||
         !token_pos || !token_seq || !seq_slots || !o_raw)
         return NNIS_ERR_ARGUMENT;
     if (seq_first_row && !seq_count) return NNIS_ERR_ARGUMENT;
-    if (dim > 256 || H > 65535 || (vdim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
-    dim3 grid(n_units, H, (vdim + 31) / 32);
-    const size_t smem = ((size_t)2 * kDeltaTile * dim + kDeltaTile * 32 + 2 * kDeltaTile) * sizeof(float);
+    if (segments && (!seq_first_row || !seq_first_segment || n_segments <= 0 || seg_len <= 0 || !seg_state ||
+                     !seg_trans || !q_run))
+        return NNIS_ERR_ARGUMENT;
+    if (dim > 256 || H > 65535 || (vdim + 31) / 32 + (dim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
     cudaError_t e;
 #define NNIS_DELTA_CASE(KL) \
-    e = launch_dependent(delta_scan_kernel<KL>, grid, 256, smem, stream, qkv, beta_g, state, token_pos, token_seq, \
-                         seq_slots, seq_first_row, seq_count, o_raw, H, G, dim, vdim)
+    e = delta_passes<KL>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
+                         n_segments, seq_first_segment, seg_len, seg_state, seg_trans, q_run, o_raw, n_units, H, G, \
+                         dim, vdim, stream)
     if (dim <= 32) NNIS_DELTA_CASE(4);
     else if (dim <= 64) NNIS_DELTA_CASE(8);
     else if (dim <= 128) NNIS_DELTA_CASE(16);

@@ -32,6 +32,7 @@ constexpr int kUmmaK = 16;
 constexpr int kMaxKSplits = 4;   // CTAs that may share a tile of the adding product
 
 enum { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_GATED = 3, GEMM_QKV = 4 };
+enum { GEMM_ACT_NONE = 0, GEMM_ACT_RELU2 = 1, GEMM_ACT_GELU_ERF = 2, GEMM_ACT_GELU_TANH = 3 };
 
 struct GemmArgs {
     const float* bias;
@@ -65,7 +66,9 @@ struct GemmArgs {
     // (it is read ahead of this kernel's wait, with the first loads of W).
     const int* tile_expert;
     int expert_rows;
-    int square_relu;  // the epilogue stores relu(x)^2 (the experts' activation) instead of x
+    // an activation in the storing epilogues: 0 none; 1 relu(x)^2 (the experts'); 2 gelu with erf,
+    // 0.5 x (1 + erf(x / sqrt 2)); 3 gelu's tanh form
+    int act;
     // GEMM_GATED with glu_limit > 0: the clamped form g' sigmoid(glu_alpha g') (u' + 1) with
     // g' = min(gate, limit), u' = up clamped to [-limit, limit], instead of silu(gate) * up
     float glu_limit, glu_alpha;
@@ -462,12 +465,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         f[i] = __uint_as_float(v[i]) + ((g.bias && nb + i < g.N) ? g.bias[nb + i] : 0.f);
-                    if (g.square_relu) {
+                    if (g.act == GEMM_ACT_RELU2) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             float a = fmaxf(f[i], 0.f);
                             f[i] = a * a;
                         }
+                    } else if (g.act == GEMM_ACT_GELU_ERF) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = 0.5f * f[i] * (1.0f + erff(f[i] * 0.70710678118654752f));
+                    } else if (g.act == GEMM_ACT_GELU_TANH) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            f[i] = 0.5f * f[i] * (1.0f + tanhf(0.79788456080286536f * (f[i] + 0.044715f * f[i] * f[i] * f[i])));
                     }
                 }
                 if (g.out_by_tma) {
@@ -605,9 +615,10 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* C,
                        const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
                        int page_size, float* split_scratch, long long split_floats,
                        unsigned* split_tickets, int split_tiles, int sm_count, int* status, int pdl,
-                       cudaStream_t stream, float glu_limit, float glu_alpha) {
+                       cudaStream_t stream, float glu_limit, float glu_alpha, int act = 0) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !C || mode < 0 || mode > 4) return NNIS_ERR_ARGUMENT;
+    if (act < 0 || act > GEMM_ACT_GELU_TANH || (act && mode != GEMM_STORE)) return NNIS_ERR_ARGUMENT;
     if (K % 8) return NNIS_ERR_UNSUPPORTED;
     if (((uintptr_t)A | (uintptr_t)W) % 16) return NNIS_ERR_ALIGNMENT;
     if (((uintptr_t)C % 16) != 0) return NNIS_ERR_ALIGNMENT;
@@ -618,7 +629,7 @@ static int gemm_tc_run(const void* A, const void* W, const float* bias, void* C,
     g.table_cols = table_cols; g.cos_t = cos_t; g.sin_t = sin_t; g.k_cache = (bf16*)k_cache;
     g.v_cache = (bf16*)v_cache; g.nq = nq; g.nkv = nkv; g.d = d; g.page_size = page_size;
     g.k_splits = 1; g.split_scratch = nullptr; g.split_tickets = nullptr;
-    g.tile_expert = nullptr; g.expert_rows = 0; g.square_relu = 0;
+    g.tile_expert = nullptr; g.expert_rows = 0; g.act = act;
     g.glu_limit = glu_limit; g.glu_alpha = glu_alpha;
     static const char* const kNames[] = {"gemm store", "gemm store_f32", "gemm add_f32", "gemm gated", "gemm qkv"};
     g.trace = trace_slot(mode >= 0 && mode <= 4 ? kNames[mode] : "gemm");
@@ -706,6 +717,15 @@ NNIS_API int nnis_gemm_tc_glu_clamp(const void* A, const void* W, const float* b
                        0, 0, 0, 0, nullptr, 0, nullptr, 0, sm_count, status, pdl, stream, limit, alpha);
 }
 
+// The storing product (mode 0) with an activation in its epilogue: out [M, N] = bf16(act(A . W^T + bias)),
+// `act` 2: gelu with erf; 3: gelu's tanh form.
+NNIS_API int nnis_gemm_tc_act(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int act,
+                              int sm_count, int* status, int pdl, cudaStream_t stream) {
+    if (act != nnis::GEMM_ACT_GELU_ERF && act != nnis::GEMM_ACT_GELU_TANH) return NNIS_ERR_ARGUMENT;
+    return gemm_tc_run(A, W, bias, C, M, N, K, 0, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr,
+                       0, 0, 0, 0, nullptr, 0, nullptr, 0, sm_count, status, pdl, stream, 0.f, 0.f, act);
+}
+
 // Grouped product on the tensor cores: C[M, N] = A[M, K] . W[tile_expert[m / 128]]^T with
 // W = [experts, N, K] bfloat16 and A's rows sorted by expert in runs padded to 128 rows
 // (`tile_expert` int32 [ceil(M / 128)], negative past the last run: those tiles are left
@@ -722,7 +742,7 @@ NNIS_API int nnis_gemm_tc_grouped(const void* A, const void* W, void* C, int M, 
     if ((M + kBM - 1) / kBM > 65535) return NNIS_ERR_UNSUPPORTED;
     GemmArgs g = {};
     g.out = C; g.M = M; g.N = N; g.K = K; g.status = status; g.k_splits = 1;
-    g.tile_expert = tile_expert; g.expert_rows = N; g.square_relu = square_relu ? 1 : 0;
+    g.tile_expert = tile_expert; g.expert_rows = N; g.act = square_relu ? GEMM_ACT_RELU2 : 0;
     g.trace = trace_slot("gemm grouped");
     const int sms = sm_count > 0 ? sm_count : 148;
     const long m_tiles = (M + kBM - 1) / kBM;

@@ -180,6 +180,7 @@ NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
 // `emit_w` [N] in bfloat16 [M, N], and per row and eight columns the sum of the output's
 // squares [M, N / 8], for a product that follows with `ss_parts` [M, K / 8]: x is then such
 // an `emit_x`, and `eps` the norm's (the kernel over tiles of rows only).
+// `act` (STORE, optional): 2 stores gelu (erf) of the sums, 3 gelu's tanh form.
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
                             float eps, const void* w, const float* bias, void* out, int M, int N,
                             int K, int epilogue, const int* token_pos, const int* token_seq,
@@ -187,10 +188,11 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
                             const float* sin_t, void* k_cache, void* v_cache, int nq, int nkv, int d,
                             int page_size, float* logits, float* best_val, int* best_idx,
                             unsigned* ticket, int* next_tokens, int* next_pos, void* emit_x,
-                            const float* emit_w, float* emit_ss, const float* ss_parts, int* status,
+                            const float* emit_w, float* emit_ss, const float* ss_parts, int act, int* status,
                             int sm_count, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
+    if (act && (epilogue != EPI_STORE || (act != 2 && act != 3))) return NNIS_ERR_ARGUMENT;
     GemvPlan plan;
     plan.kc = K;
     int pro = hidden ? PRO_NORM : ss_parts ? PRO_SCALED : PRO_PLAIN;
@@ -227,7 +229,7 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
     a.logits = logits; a.best_val = best_val; a.best_idx = best_idx; a.ticket = ticket;
     a.next_tokens = next_tokens; a.next_pos = next_pos;
     a.emit_x = nullptr; a.emit_w = emit_w; a.emit_ss = emit_ss;
-    a.ss_parts = ss_parts; a.ss_units = K / 8;
+    a.ss_parts = ss_parts; a.ss_units = K / 8; a.act = act;
     a.ldx = K; a.ldw = K; a.kc = plan.kc; a.out_is_hot = 0;
     a.release_early = (pdl & 2) && slices == 1 ? 1 : 0;
     a.K = K / slices;

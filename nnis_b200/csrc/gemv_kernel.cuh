@@ -87,7 +87,16 @@ struct GemvArgs {
     // PRO_SCALED prologue: those shares of the rows' sums of squares, [M, ss_units]
     const float* ss_parts;
     int ss_units;
+    // STORE epilogue, optional: an activation on the sums before they are rounded; 0 none, 2 gelu with
+    // erf, 3 gelu's tanh form (the codes of the tensor-core product's storing epilogue)
+    int act;
 };
+
+__device__ __forceinline__ float gemv_act(float z, int act) {
+    if (act == 2) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    if (act == 3) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+    return z;
+}
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
@@ -316,6 +325,10 @@ __device__ __forceinline__ void epi_finish(const GemvArgs& a, int unit, int row0
             float v0 = v[hrow * 2] + b0v, v1 = v[hrow * 2 + 1] + b1v;
             size_t o = (size_t)m * a.N + n0;
             if (EPI == EPI_STORE) {
+                if (a.act) {
+                    v0 = gemv_act(v0, a.act);
+                    v1 = gemv_act(v1, a.act);
+                }
                 *reinterpret_cast<uint32_t*>(reinterpret_cast<bf16*>(a.out) + o) = pack_bf16(v0, v1);
             } else if (EPI == EPI_STORE_F32) {
                 *reinterpret_cast<float2*>(reinterpret_cast<float*>(a.out) + o) = make_float2(v0, v1);

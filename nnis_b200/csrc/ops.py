@@ -231,6 +231,8 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
 
 
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
+# activations that the storing epilogues of the bfloat16 products can apply (gelu with erf, its tanh form)
+GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH = 2, 3
 # programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
 PDL = 0 if os.environ.get("NNIS_PDL", "1") == "0" else 1
 # The QKV projection of a decode step lets attention_decode_tma start with it instead of after
@@ -344,7 +346,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               scratch: Optional[torch.Tensor] = None, next_tokens: Optional[torch.Tensor] = None,
               next_pos: Optional[torch.Tensor] = None, release_early: bool = False,
               rows_kernel: bool = True, emit: Optional[tuple] = None,
-              shares: Optional[torch.Tensor] = None) -> None:
+              shares: Optional[torch.Tensor] = None, act: int = 0) -> None:
     """A decode-step projection with its prologue and epilogue fused (at most 64
     rows).  The input is ``x`` (bfloat16 [m, k]) or ``hidden`` (float32 residual
     rows, normed with ``norm_weight``/``eps`` on the way in; ``rows`` picks them).
@@ -397,6 +399,8 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               "gemv: emit shares float32 [m, n / 8]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
+    _need(act == 0 or (epilogue == EPI_STORE and act in (GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH)),
+          "gemv: an activation goes with the storing epilogue")
     if epilogue == EPI_STORE:
         _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n), "gemv: out bfloat16 [m, n]")
     elif epilogue in (EPI_STORE_F32, EPI_ADD_F32):
@@ -438,7 +442,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
         _ptr(page_table), cols, _ptr(cos), _ptr(sin), _ptr(k_cache), _ptr(v_cache), heads, kv_heads,
         head_dim, page_size, _ptr(logits), ctypes.c_void_p(best_val), ctypes.c_void_p(best_idx),
         ctypes.c_void_p(ticket), _ptr(next_tokens), _ptr(next_pos), _ptr(emit_x), _ptr(emit_w),
-        _ptr(emit_ss), _ptr(shares), _ptr(status_word(w.device)),
+        _ptr(emit_ss), _ptr(shares), act, _ptr(status_word(w.device)),
         sm_count(w.device),
         PDL | (2 if release_early and PDL and EARLY_RELEASE else 0) | (0 if rows_kernel else 4), _stream()),
         "gemv_bf16",
@@ -887,6 +891,21 @@ def gemm_tc_glu_clamp(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Ten
     _check(_lib().nnis_gemm_tc_glu_clamp(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, ctypes.c_float(limit),
                                          ctypes.c_float(alpha), sm_count(a.device), _ptr(status_word(a.device)),
                                          PDL, _stream()), "gemm_tc_glu_clamp")
+
+
+def gemm_tc_act(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, act: int) -> None:
+    """The storing tensor-core product with an activation in its epilogue: out bfloat16 [m, n] =
+    act(a . w^T + bias); ``GEMM_ACT_GELU_ERF`` or ``GEMM_ACT_GELU_TANH``."""
+    _cuda(a, w, bias, out)
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a.dtype == w.dtype == torch.bfloat16 and w.shape[1] == k, "gemm_tc_act: bfloat16 a [m, k], w [n, k]")
+    _need(gemm_tc_takes(m, n, k), f"gemm_tc_act: shape m={m} n={n} k={k} is not taken")
+    _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n), "gemm_tc_act: out bfloat16 [m, n]")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm_tc_act: bias float32 [n]")
+    _check(_lib().nnis_gemm_tc_act(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, act, sm_count(a.device),
+                                   _ptr(status_word(a.device)), PDL, _stream()), "gemm_tc_act")
 
 
 GEMM_SPLIT_K = os.environ.get("NNIS_GEMM_SPLIT_K", "1") == "1"
@@ -1728,20 +1747,39 @@ def delta_prep(a: torch.Tensor, conv_w: torch.Tensor, tail: torch.Tensor, a_log:
 def delta_scan(qkv: torch.Tensor, beta_g: torch.Tensor, state: torch.Tensor, token_pos: torch.Tensor,
                token_seq: torch.Tensor, seq_slots: torch.Tensor, seq_first_row: Optional[torch.Tensor],
                seq_count: Optional[torch.Tensor], o_raw: torch.Tensor, heads: int, kv_heads: int, dim: int,
-               vdim: int) -> None:
+               vdim: int, segments: Optional[torch.Tensor] = None, seq_first_segment: Optional[torch.Tensor] = None,
+               seg_len: int = 0, seg_state: Optional[torch.Tensor] = None, seg_trans: Optional[torch.Tensor] = None,
+               q_run: Optional[torch.Tensor] = None) -> None:
     """The gated delta rule over the step's tokens, from and into ``state`` float32
-    [slots, heads, dim, vdim]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q."""
+    [slots, heads, dim, vdim]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.  With
+    ``segments`` (``scan_segments``) a prompt step's sequences are cut into runs of ``seg_len`` tokens that
+    are worked side by side; scratch ``seg_state`` float32 [runs, heads, dim, vdim], ``seg_trans``
+    [runs, heads, dim, dim] and ``q_run`` [n, heads, dim]."""
     _seq_tables(token_pos, token_seq, seq_slots, seq_first_row, seq_count)
-    _cuda(qkv, beta_g, state, o_raw)
+    _cuda(qkv, beta_g, state, o_raw, segments, seq_first_segment, seg_state, seg_trans, q_run)
     n = qkv.shape[0]
     _need(qkv.dtype == beta_g.dtype == state.dtype == o_raw.dtype == torch.float32, "delta_scan: float32")
     _need(qkv.shape[1] == 2 * kv_heads * dim + heads * vdim and tuple(beta_g.shape) == (n, 2 * heads)
           and tuple(state.shape[1:]) == (heads, dim, vdim) and o_raw.numel() >= n * heads * vdim,
           "delta_scan: qkv [n, channels], beta_g [n, 2 heads], state [slots, heads, dim, vdim]")
     units = seq_first_row.numel() if seq_first_row is not None else n
+    n_segments = 0
+    if segments is not None:
+        n_segments = segments.shape[0]
+        _need(seq_first_row is not None and seq_first_segment is not None and seg_len > 0
+              and all(t is not None and t.dtype == torch.float32 for t in (seg_state, seg_trans, q_run))
+              and seg_state.numel() >= n_segments * heads * dim * vdim
+              and seg_trans.numel() >= n_segments * heads * dim * dim and q_run.numel() >= n * heads * dim
+              and segments.dtype == seq_first_segment.dtype == torch.int32,
+              "delta_scan: runs need a prompt step, their tables and scratch")
     _check(_lib().nnis_delta_scan(_ptr(qkv), _ptr(beta_g), _ptr(state), _ptr(token_pos), _ptr(token_seq),
-                                  _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(o_raw), units, heads,
-                                  kv_heads, dim, vdim, _stream()), "delta_scan")
+                                  _ptr(seq_slots), _ptr(seq_first_row), _ptr(seq_count), _ptr(segments), n_segments,
+                                  _ptr(seq_first_segment), seg_len, _ptr(seg_state), _ptr(seg_trans), _ptr(q_run),
+                                  _ptr(o_raw), units, heads, kv_heads, dim, vdim, _stream()),
+           "delta_scan", 3 if segments is not None else 1)
+
+
+DELTA_SEGMENT = int(os.environ.get("NNIS_DELTA_SEGMENT", "128"))  # tokens of a run of the delta rule; 0: no runs
 
 
 def delta_finish(o_raw: torch.Tensor, gate_rows: torch.Tensor, gate_off: int, weight: torch.Tensor,

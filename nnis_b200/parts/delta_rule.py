@@ -15,6 +15,11 @@ heads of v (``vdim`` values; head i reads q/k head i // (heads / kv_heads)):
 * Each head's o is divided by its root mean square (``eps``), multiplied by a weight per value
   that all heads share and by silu(W_g h), and W_o adds the result into the residual rows.
 
+The recurrence is linear in the state: S_after = P S_before + S_run over a stretch of tokens, with P the
+product of the tokens' g (I - beta k k^T).  A long prompt is cut into runs of 128 tokens that are walked side
+by side from nothing (which also yields P, as the fate of an identity matrix under the same walk), put
+together in order, and finished by one product a run.
+
 S [heads, dim, vdim] and the convolutions' last taps - 1 inputs are float32 in the cache's state
 area, one of each per slot, zero when a slot is taken, so a later portion of a prompt or a single
 token goes on from what the tokens before left.  One product makes all six projections in
@@ -100,6 +105,17 @@ class GatedDeltaRule(Part):
         return 2.0 * sum(counts) * (W * self.w_in.shape[0] + H * self.vdim * W + self.channels * self.taps
                                     + 3 * H * self.dim * self.vdim)
 
+    SEGMENTS, FIRST_SEGMENT = "delta/segments", "delta/first_segment"
+
+    def step_tables(self, counts, starts, have=()):
+        """Prompt steps with a sequence longer than two runs: the runs of every sequence, worked side
+        by side (the same list for every delta rule layer of the model)."""
+        seg = ops.DELTA_SEGMENT
+        if seg <= 0 or max(counts) <= 2 * seg or self.SEGMENTS in have:
+            return {}
+        segments, first = ops.scan_segments(counts, seg)
+        return {self.SEGMENTS: segments, self.FIRST_SEGMENT: first}
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, cache: StateView) -> None:
         n = residual.shape[0]
         H, G, ws = self.heads, self.kv_heads, ctx.workspace
@@ -111,8 +127,14 @@ class GatedDeltaRule(Part):
                        ctx.seq_slots, ctx.seq_first_row, ctx.seq_count, qkv, beta_g, H, G, self.dim, self.vdim,
                        self.unit_eps, self.dim ** -0.5)
         o_raw = ws.get("delta_o", (n, H * self.vdim), torch.float32)
+        segments = ctx.tables.get(self.SEGMENTS) if not ctx.decode else None
+        runs = segments.shape[0] if segments is not None else 0
         ops.delta_scan(qkv, beta_g, cache.state, ctx.token_pos, ctx.token_seq, ctx.seq_slots, ctx.seq_first_row,
-                       ctx.seq_count, o_raw, H, G, self.dim, self.vdim)
+                       ctx.seq_count, o_raw, H, G, self.dim, self.vdim, segments=segments,
+                       seq_first_segment=ctx.tables.get(self.FIRST_SEGMENT), seg_len=ops.DELTA_SEGMENT,
+                       seg_state=ws.get("delta_run_state", (runs, H, self.dim, self.vdim), torch.float32) if runs else None,
+                       seg_trans=ws.get("delta_run_trans", (runs, H, self.dim, self.dim), torch.float32) if runs else None,
+                       q_run=ws.get("delta_run_q", (n, H, self.dim), torch.float32) if runs else None)
         gated = ws.get("delta_gated", (n, H * self.vdim), self.dtype)
         ops.delta_finish(o_raw, rows, self.channels, self.norm, ctx.token_pos, gated, H, self.vdim, self.eps)
         linear(gated, self.w_o, None, residual, ADD_F32, ws, decode=ctx.decode)

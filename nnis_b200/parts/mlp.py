@@ -130,12 +130,15 @@ class GatedMLP(Part):
 
 
 class DenseMLP(Part):
-    """Feed-forward without a gate: down(act(up(x))), added to the residual.  The first product
-    leaves float32; the activation kernel rounds once to the operand dtype.
+    """Feed-forward without a gate: down(act(up(x))), added to the residual.  The activation is
+    applied to the first product's float32 sums and rounded once to the operand dtype: in the
+    product's own epilogue in bfloat16 (tensor-core and decode kernels), by a kernel of its own
+    otherwise.
 
     params: hidden_size, intermediate_size, activation ("gelu": 0.5 z (1 + erf(z / sqrt 2));
     "gelu_tanh": 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), names {up, down}."""
     ACTIVATIONS = {"gelu": ops.GELU_ERF, "gelu_tanh": ops.GELU_TANH}
+    FUSED = {ops.GELU_ERF: ops.GEMM_ACT_GELU_ERF, ops.GELU_TANH: ops.GEMM_ACT_GELU_TANH}  # the products' codes
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -165,10 +168,18 @@ class DenseMLP(Part):
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         n = residual.shape[0]
         ws = ctx.workspace
-        up = ws.get("mlp_up", (n, self.inter), torch.float32)
-        linear(x, self.w_up, None, up, STORE_F32, decode=ctx.decode)
+        kind = self.ACTIVATIONS[self.activation]
         act = ws.get("act", (n, self.inter), self.dtype)
-        ops.act_rows(up, act, self.ACTIVATIONS[self.activation])
+        # bfloat16: the activation rides in the first product's epilogue (the float32 sums, rounded once)
+        if self.dtype == torch.bfloat16 and ctx.decode and ops.gemv_pays(n, self.inter, self.hidden, ops.EPI_STORE,
+                                                                         x.device):
+            ops.gemv_bf16(self.w_up, None, act, ops.EPI_STORE, x=x, act=self.FUSED[kind])
+        elif self.dtype == torch.bfloat16 and ops.gemm_tc_takes(n, self.inter, self.hidden):
+            ops.gemm_tc_act(x, self.w_up, None, act, self.FUSED[kind])
+        else:
+            up = ws.get("mlp_up", (n, self.inter), torch.float32)
+            linear(x, self.w_up, None, up, STORE_F32, decode=ctx.decode)
+            ops.act_rows(up, act, kind)
         linear(act, self.w_down, None, residual, ADD_F32, ws, decode=ctx.decode)
 
 

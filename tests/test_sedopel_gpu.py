@@ -178,6 +178,70 @@ def test_delta_rule_kernels_in_portions_against_the_recurrence(H, G, dim, vdim, 
         assert torch.equal(tail[2, :, :].cpu(), rows_all[0][45 - (taps - 1):, :channels])
 
 
+@pytest.mark.parametrize("H, G, dim, vdim", [(2, 1, 64, 64), (4, 2, 24, 40), (3, 3, 10, 7), (2, 2, 136, 33), (1, 1, 256, 70),
+                                            (2, 1, 128, 128)])
+def test_delta_rule_runs_side_by_side_agree_with_the_walk_in_order(H, G, dim, vdim):
+    """A step of three sequences (300, 131 and 64 tokens) that go on from states which an earlier
+    step left: cut into runs of 64 tokens and put together, against the same kernel walking every
+    sequence in order, and that against the recurrence in float64.  The decays reach from fast to
+    almost none, so the first run's tokens still count in the last."""
+    from nnis_b200.csrc import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(dim + vdim)
+    channels = 2 * G * dim + H * vdim
+    counts = (300, 131, 64)
+    n = sum(counts)
+    unit = lambda x: x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    q = unit(torch.randn(n, G, dim, generator=g)) * dim ** -0.5
+    k = unit(torch.randn(n, G, dim, generator=g))
+    v = torch.randn(n, H, vdim, generator=g)
+    qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], 1).to(dev)
+    beta = torch.rand(n, H, generator=g)
+    decay = torch.exp(-torch.exp(torch.empty(H).uniform_(-7, -1, generator=g))[None, :] * torch.rand(n, H, generator=g) * 2)
+    beta_g = torch.cat([beta, decay], 1).to(dev)
+    begin = torch.randn(4, H, dim, vdim, generator=g) * 0.3
+    pos = torch.cat([torch.arange(5, 5 + c) for c in counts]).to(torch.int32).to(dev)
+    seq = torch.cat([torch.full((c,), i) for i, c in enumerate(counts)]).to(torch.int32).to(dev)
+    slots = torch.tensor([3, 0, 1], dtype=torch.int32, device=dev)
+    first = torch.tensor([0, 300, 431], dtype=torch.int32, device=dev)
+    count = torch.tensor(counts, dtype=torch.int32, device=dev)
+    outs, states = [], []
+    for runs in (False, True):
+        state = begin.to(dev).clone()
+        o_raw = torch.zeros(n, H * vdim, device=dev)
+        extra = {}
+        if runs:
+            segments, first_segment = ops.scan_segments(counts, 64)
+            assert segments.shape[0] == 5 + 3 + 1
+            extra = dict(segments=torch.from_numpy(segments).to(dev), seq_first_segment=torch.from_numpy(first_segment).to(dev),
+                         seg_len=64, seg_state=torch.full((9, H, dim, vdim), 7.0, device=dev),
+                         seg_trans=torch.full((9, H, dim, dim), 7.0, device=dev), q_run=torch.full((n, H, dim), 7.0, device=dev))
+        ops.delta_scan(qkv, beta_g, state, pos, seq, slots, first, count, o_raw, H, G, dim, vdim, **extra)
+        outs.append(o_raw.cpu().double().reshape(n, H, vdim))
+        states.append(state.cpu().double())
+    want_o = torch.zeros(n, H, vdim, dtype=torch.float64)
+    want_s = begin.double().clone()
+    at = 0
+    for i, c in enumerate(counts):
+        for hh in range(H):
+            j = hh // (H // G)
+            S = begin[int(slots[i]), hh].double().clone()
+            for t in range(at, at + c):
+                S = decay[t, hh].double() * S
+                u = beta[t, hh].double() * (v[t, hh].double() - S.T @ k[t, j].double())
+                S = S + torch.outer(k[t, j].double(), u)
+                want_o[t, hh] = S.T @ q[t, j].double()
+            want_s[int(slots[i]), hh] = S
+        at += c
+    scale_o, scale_s = float(want_o.abs().max()), float(want_s.abs().max())
+    for got_o, got_s in zip(outs, states):
+        assert float((got_o - want_o).abs().max()) < 2e-5 * scale_o, float((got_o - want_o).abs().max()) / scale_o
+        assert float((got_s - want_s).abs().max()) < 2e-5 * scale_s
+        assert torch.equal(got_s[2], begin[2].double())  # the slot that no sequence holds
+    # the first run's tokens count at the end: without them the last outputs of the long sequence differ clearly
+    assert float(decay[:300].max()) > 0.999
+
+
 # ---- whole models ------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["softmax", "heads64", "lightning", "delta", "dense"])
