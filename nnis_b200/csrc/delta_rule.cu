@@ -17,8 +17,8 @@
 //                  q_scale; beta = sigmoid(b); g = exp(-exp(A_log) * softplus(a + dt_bias)).
 //   delta_conv_tail  moves the convolutions' state on by the step's inputs.
 //   delta_scan     a CTA per (sequence, head, 32 columns of vdim) walks the step's tokens in order.
-//                  A column of S never meets another, so a column is owned by KS = 8 neighbouring
-//                  lanes that hold dim / 8 of its values each in registers.  Since
+//                  A column of S never meets another, so a column is owned by KS (1 to 8) neighbouring
+//                  lanes that hold 32 of its values each in registers.  Since
 //                  o = g S^T q + u (k . q), the sums S^T k and S^T q are reduced together, one round
 //                  of shuffles a token, and k . q is made once a token for all columns.  Tokens come
 //                  16 at a time through shared memory.
@@ -132,7 +132,7 @@ delta_conv_tail_kernel(const float* __restrict__ a, float* __restrict__ tail, co
 constexpr int kDeltaTile = 16;  // tokens a trip through shared memory
 constexpr int kDeltaKS = 8;     // lanes that share a column of the state
 
-// KL: state values a thread holds (dim <= 8 KL).  qkv float32 [n, 2 G dim + H vdim]; beta_g float32 [n, 2 H].
+// KL: state values a thread holds, KS: threads to a column (dim <= KL KS).  qkv float32 [n, 2 G dim + H vdim]; beta_g float32 [n, 2 H].
 // PASS 0: a unit is a sequence (or, without the sequences' tables, a row): its tokens of the step in order, from and
 //         into the slot's state.
 // PASS 1: a unit is a run of `seg_len` tokens (`segments`: sequence, first token), worked from nothing.  The recurrence
@@ -142,40 +142,49 @@ constexpr int kDeltaKS = 8;     // lanes that share a column of the state
 //         them hold `dim` columns that start as the identity and see values of zero: they end as P (seg_trans
 //         [runs, H, dim, dim]), and their read-out at token t is P_t^T q_t (q_run [n, H, dim]), with which the part
 //         of o_t that comes from before the run is (P_t^T q_t)^T S_before: a product, no second walk (delta_apply).
-// A thread's KL state values of its column: key channel of register r in the eighth `part`.  Four neighbouring
-// registers are four neighbouring channels, and the eight parts' fours lie side by side: a token's q and k come from
-// shared memory 16 bytes a load, eight lanes reading 128 bytes in a row.
+// The kernels after the walk (delta_prefix, delta_apply) hold a column's values in eight lanes: key channel of
+// register r in the eighth `part`.
 __device__ __forceinline__ int delta_channel(int r, int part) { return (r >> 2) * 32 + part * 4 + (r & 3); }
 
-// rows of `dim` values from global memory into rows of `stride` floats of shared memory: the loads of a batch are all
-// issued before the first store (shared memory may alias anything, as far as the compiler knows)
-template <typename Src>
-__device__ __forceinline__ void delta_stage(float* dst, int stride, int rows, int dim, Src src) {
-    const int total = rows * dim;
-    for (int base = 0; base < total; base += 256 * 4) {
+// rows of `width` values from global memory into rows of `stride` floats of shared memory, zeros from `width` up to
+// W (a constant, so that a thread finds its row and column without a division): the loads of a batch are all issued
+// before the first store (shared memory may alias anything, as far as the compiler knows)
+template <int W, int NT, typename Src>
+__device__ __forceinline__ void delta_stage(float* dst, int stride, int rows, int width, Src src) {
+    const int total = rows * W;
+    for (int base = 0; base < total; base += NT * 4) {
         float v[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int it = base + u * 256 + (int)threadIdx.x;
-            v[u] = it < total ? src(it / dim, it % dim) : 0.f;
+            const int it = base + u * NT + (int)threadIdx.x;
+            v[u] = (it < total && it % W < width) ? src(it / W, it % W) : 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-            const int it = base + u * 256 + (int)threadIdx.x;
-            if (it < total) dst[(it / dim) * stride + it % dim] = v[u];
+            const int it = base + u * NT + (int)threadIdx.x;
+            if (it < total) dst[(it / W) * stride + it % W] = v[u];
         }
     }
 }
 
-template <int KL, int PASS>
-__global__ void __launch_bounds__(256)
+// The walk itself: KS lanes share a column and hold KL = DP / KS of its values each, a CTA of 32 KS threads holds 32
+// columns.  Few lanes a column mean few shuffles a token (log2 KS rounds for the two sums) beside its 3 KL multiply-adds,
+// so KS is the smallest that leaves a thread 32 values: 2 for keys of 64, 4 for 128, 8 for 256.  Register r of lane
+// `part` holds channel (r / 4) 4 KS + 4 part + r % 4: a column's lanes read a token's q and k 16 bytes a load, side by
+// side.
+template <int KS>
+__device__ __forceinline__ int scan_channel(int r, int part) { return (r >> 2) * (4 * KS) + part * 4 + (r & 3); }
+
+template <int KL, int KS, int PASS>
+__global__ void __launch_bounds__(32 * KS)
 delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_g, float* __restrict__ state,
                   const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                   const int* __restrict__ seq_slots, const int* __restrict__ seq_first_row,
                   const int* __restrict__ seq_count, const int* __restrict__ segments, int seg_len,
                   float* __restrict__ seg_state, float* __restrict__ seg_trans, float* __restrict__ q_run,
                   float* __restrict__ o_raw, int H, int G, int dim, int vdim) {
-    constexpr int KS = kDeltaKS, TT = kDeltaTile, DP = KL * KS;  // DP: dim rounded up, the tile's row
+    constexpr int TT = kDeltaTile, DP = KL * KS, NT = 32 * KS;  // DP: dim rounded up, the tile's row
+    static_assert(NT >= TT && KL % 4 == 0, "a thread per token of a tile; channels in fours");
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;              // [TT][DP], zero past dim
     float* ks = qs + TT * DP;      // [TT][DP]
@@ -184,7 +193,6 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
     float* gs = bs + TT;           // [TT] decay
     float* kqs = gs + TT;          // [TT] k . q
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < 2 * TT * DP; i += 256) smem[i] = 0.f;
     pdl_wait();
     pdl_launch_dependents();
     const int unit = blockIdx.x, h = blockIdx.y;
@@ -204,11 +212,12 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
         slot = seq_slots[token_seq[unit]];
     }
     if (count <= 0) return;
-    const int part = tid & (KS - 1);               // which eighth of the column
+    const int part = tid & (KS - 1);               // which share of the column
+    const int cg = tid / KS;                       // which of the CTA's 32 columns
     const int value_tiles = (vdim + 31) / 32;
     const bool trans = PASS == 1 && (int)blockIdx.z >= value_tiles;
     const int tile0 = (trans ? (int)blockIdx.z - value_tiles : (int)blockIdx.z) * 32;
-    const int col = tile0 + (tid >> 3);            // the column of the state
+    const int col = tile0 + cg;                    // the column of the state
     const int ncols = trans ? dim : vdim;
     const bool live = col < ncols;
     const int kv = h / (H / G);
@@ -219,17 +228,18 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
     float s[KL];
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
-        const int d = delta_channel(r, part);
+        const int d = scan_channel<KS>(r, part);
         if (PASS == 0) s[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
         else s[r] = (trans && live && d == col) ? 1.f : 0.f;
     }
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int cnt = min(TT, count - t0);
         const float* rows = qkv + (size_t)(first + t0) * cols;
-        __syncthreads();  // the tile before is read (and the tiles are zero past dim)
-        delta_stage(qs, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)kv * dim + d]; });
-        delta_stage(ks, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)(G + kv) * dim + d]; });
-        delta_stage(vs, 32, cnt, 32, [&](int i, int c) {
+        __syncthreads();  // the tile before is read
+        delta_stage<DP, NT>(qs, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)kv * dim + d]; });
+        delta_stage<DP, NT>(ks, DP, cnt, dim,
+                            [&](int i, int d) { return rows[(size_t)i * cols + (size_t)(G + kv) * dim + d]; });
+        delta_stage<32, NT>(vs, 32, cnt, 32, [&](int i, int c) {
             return (!trans && tile0 + c < vdim) ? rows[(size_t)i * cols + 2 * G * dim + (size_t)h * vdim + tile0 + c] : 0.f;
         });
         if (tid < cnt) {
@@ -237,9 +247,9 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
             gs[tid] = beta_g[(size_t)(first + t0 + tid) * 2 * H + H + h];
         }
         __syncthreads();
-        for (int i = warp; i < cnt; i += 8) {  // k . q is the same for every column
+        for (int i = warp; i < cnt; i += NT / 32) {  // k . q is the same for every column
             float kq = 0.f;
-            for (int d = lane; d < dim; d += 32) kq = fmaf(ks[i * DP + d], qs[i * DP + d], kq);
+            for (int d = lane; d < DP; d += 32) kq = fmaf(ks[i * DP + d], qs[i * DP + d], kq);
             kq = warp_sum(kq);
             if (lane == 0) kqs[i] = kq;
         }
@@ -247,31 +257,32 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
         for (int i = 0; i < cnt; ++i) {
             const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * 4);
             const float4* k4 = reinterpret_cast<const float4*>(ks + i * DP + part * 4);
-            float sk = 0.f, sq = 0.f;
+            float sk[2] = {0.f, 0.f}, sq[2] = {0.f, 0.f};  // two chains each: a sum of KL terms is long
             float kr[KL];
 #pragma unroll
             for (int r4 = 0; r4 < KL / 4; ++r4) {
-                const float4 kk = k4[r4 * 8], qq = q4[r4 * 8];
+                const float4 kk = k4[r4 * KS], qq = q4[r4 * KS];
                 const float kx[4] = {kk.x, kk.y, kk.z, kk.w}, qx[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     kr[r4 * 4 + e] = kx[e];
-                    sk = fmaf(s[r4 * 4 + e], kx[e], sk);
-                    sq = fmaf(s[r4 * 4 + e], qx[e], sq);
+                    sk[e & 1] = fmaf(s[r4 * 4 + e], kx[e], sk[e & 1]);
+                    sq[e & 1] = fmaf(s[r4 * 4 + e], qx[e], sq[e & 1]);
                 }
             }
+            float sks = sk[0] + sk[1], sqs = sq[0] + sq[1];
 #pragma unroll
             for (int o = KS / 2; o > 0; o >>= 1) {
-                sk += __shfl_xor_sync(0xffffffffu, sk, o);
-                sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                sks += __shfl_xor_sync(0xffffffffu, sks, o);
+                sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
             }
             // o = (g S + k u^T)^T q = g S^T q + u (k . q), with S the state before the token
             const float g = gs[i];
-            const float u = bs[i] * (vs[i * 32 + (tid >> 3)] - g * sk);
+            const float u = bs[i] * (vs[i * 32 + cg] - g * sks);
 #pragma unroll
             for (int r = 0; r < KL; ++r) s[r] = fmaf(kr[r], u, g * s[r]);
             if (part == 0 && live) {
-                const float o = fmaf(u, kqs[i], g * sq);
+                const float o = fmaf(u, kqs[i], g * sqs);
                 if (trans) q_run[((size_t)(first + t0 + i) * H + h) * dim + col] = o;
                 else o_raw[((size_t)(first + t0 + i) * H + h) * vdim + col] = o;
             }
@@ -279,7 +290,7 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
     }
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
-        const int d = delta_channel(r, part);
+        const int d = scan_channel<KS>(r, part);
         if (live && d < dim) S[(size_t)d * ncols + col] = s[r];
     }
 }
@@ -333,7 +344,7 @@ delta_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots
         for (int e0 = 0; e0 < dim; e0 += EC) {
             const int en = min(EC, dim - e0);
             __syncthreads();  // cs is whole; the chunk before is read
-            delta_stage(ps, EC + 1, dim, en, [&](int d, int ee) { return P[(size_t)d * dim + e0 + ee]; });
+            delta_stage<EC, 256>(ps, EC + 1, dim, en, [&](int d, int ee) { return P[(size_t)d * dim + e0 + ee]; });
             __syncthreads();
             for (int ee = 0; ee < en; ++ee) {
                 const float c = cs[(e0 + ee) * 32 + cg];
@@ -387,7 +398,7 @@ delta_apply_kernel(const float* __restrict__ q_run, const float* __restrict__ se
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int cnt = min(TT, count - t0);
         __syncthreads();
-        delta_stage(qs, DP, cnt, dim, [&](int i, int d) { return q_run[((size_t)(first + t0 + i) * H + h) * dim + d]; });
+        delta_stage<DP, 256>(qs, DP, cnt, dim, [&](int i, int d) { return q_run[((size_t)(first + t0 + i) * H + h) * dim + d]; });
         __syncthreads();
 #pragma unroll 4
         for (int i = 0; i < cnt; ++i) {
@@ -480,7 +491,7 @@ NNIS_API int nnis_delta_prep(const float* a, const float* conv_w, float* tail, c
 
 namespace nnis {
 
-template <int KL>
+template <int KL, int SKL, int SKS>
 static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* state, const int* token_pos,
                                 const int* token_seq, const int* seq_slots, const int* seq_first_row,
                                 const int* seq_count, const int* segments, int n_segments,
@@ -488,13 +499,13 @@ static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* st
                                 float* q_run, float* o_raw, int n_units, int H, int G, int dim, int vdim,
                                 cudaStream_t stream) {
     const int value_tiles = (vdim + 31) / 32;
-    const size_t smem = ((size_t)2 * kDeltaTile * KL * kDeltaKS + kDeltaTile * 32 + 3 * kDeltaTile) * sizeof(float);
+    const size_t smem = ((size_t)2 * kDeltaTile * SKL * SKS + kDeltaTile * 32 + 3 * kDeltaTile) * sizeof(float);
     if (!segments)
-        return launch_dependent(delta_scan_kernel<KL, 0>, dim3(n_units, H, value_tiles), 256, smem, stream, qkv,
+        return launch_dependent(delta_scan_kernel<SKL, SKS, 0>, dim3(n_units, H, value_tiles), 32 * SKS, smem, stream, qkv,
                                 beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments,
                                 seg_len, seg_state, seg_trans, q_run, o_raw, H, G, dim, vdim);
-    cudaError_t e = launch_dependent(delta_scan_kernel<KL, 1>, dim3(n_segments, H, value_tiles + (dim + 31) / 32),
-                                     256, smem, stream, qkv, beta_g, state, token_pos, token_seq, seq_slots,
+    cudaError_t e = launch_dependent(delta_scan_kernel<SKL, SKS, 1>, dim3(n_segments, H, value_tiles + (dim + 31) / 32),
+                                     32 * SKS, smem, stream, qkv, beta_g, state, token_pos, token_seq, seq_slots,
                                      seq_first_row, seq_count, segments, seg_len, seg_state, seg_trans, q_run, o_raw,
                                      H, G, dim, vdim);
     if (e != cudaSuccess) return e;
@@ -533,14 +544,14 @@ NNIS_API int nnis_delta_scan(const float* qkv, const float* beta_g, float* state
         return NNIS_ERR_ARGUMENT;
     if (dim > 256 || H > 65535 || (vdim + 31) / 32 + (dim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
     cudaError_t e;
-#define NNIS_DELTA_CASE(KL) \
-    e = delta_passes<KL>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
+#define NNIS_DELTA_CASE(KL, SKL, SKS) \
+    e = delta_passes<KL, SKL, SKS>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
                          n_segments, seq_first_segment, seg_len, seg_state, seg_trans, q_run, o_raw, n_units, H, G, \
                          dim, vdim, stream)
-    if (dim <= 32) NNIS_DELTA_CASE(4);
-    else if (dim <= 64) NNIS_DELTA_CASE(8);
-    else if (dim <= 128) NNIS_DELTA_CASE(16);
-    else NNIS_DELTA_CASE(32);
+    if (dim <= 32) NNIS_DELTA_CASE(4, 32, 1);
+    else if (dim <= 64) NNIS_DELTA_CASE(8, 32, 2);
+    else if (dim <= 128) NNIS_DELTA_CASE(16, 32, 4);
+    else NNIS_DELTA_CASE(32, 32, 8);
 #undef NNIS_DELTA_CASE
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
