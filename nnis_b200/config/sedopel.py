@@ -75,16 +75,24 @@ def _check_softmax(m: Mapping[str, Any], where: str) -> None:
     _float(rot, "base", where + ".rot")
 
 
+def _decays(m: Mapping[str, Any], heads: int, where: str) -> Tuple[float, ...]:
+    """One decay per head; a single number stands for all heads."""
+    decay = m.get("decay")
+    if not isinstance(decay, list):
+        decay = [decay] * heads
+    if len(decay) != heads:
+        raise ConfigError(f"config.json: {where}.decay must be one number or one per head ({heads})")
+    for d in decay:
+        if isinstance(d, bool) or not isinstance(d, (int, float)) or not 0 < d <= 1:
+            raise ConfigError(f"config.json: {where}.decay values lie in (0, 1]; got {d!r}")
+    return tuple(float(d) for d in decay)
+
+
 def _check_lightning(m: Mapping[str, Any], where: str) -> None:
     heads = _int(m, "heads", where)
     _int(m, "dim", where)
     _int(m, "vdim", where)
-    decay = m.get("decay")
-    if not isinstance(decay, list) or len(decay) != heads:
-        raise ConfigError(f"config.json: {where}.decay must list one number per head ({heads})")
-    for d in decay:
-        if isinstance(d, bool) or not isinstance(d, (int, float)) or not 0 < d <= 1:
-            raise ConfigError(f"config.json: {where}.decay values lie in (0, 1]; got {d!r}")
+    _decays(m, heads, where)
 
 
 def _check_delta(m: Mapping[str, Any], where: str) -> None:
@@ -171,7 +179,7 @@ class SedopelConfig:
     def _lightning(self, m: Mapping[str, Any], stem: str) -> PartSpec:
         return PartSpec("retention", {
             "hidden_size": self.width, "heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"],
-            "decay": tuple(float(d) for d in m["decay"]), "eps": self.norm_eps,
+            "decay": _decays(m, int(m["heads"]), "mixer.right"), "eps": self.norm_eps,
             "position": PartSpec("rope_frequencies", {"dims": 0, "base": 1.0}),
             "activation": "silu", "key_scale": 1.0, "norm": "joined", "gate": "sigmoid", "leaf": "",
             "names": {"q": f"{stem}.q", "k": f"{stem}.k", "v": f"{stem}.v", "g": f"{stem}.g", "o": f"{stem}.o",

@@ -130,7 +130,8 @@ delta_conv_tail_kernel(const float* __restrict__ a, float* __restrict__ tail, co
 }
 
 constexpr int kDeltaTile = 16;  // tokens a trip through shared memory
-constexpr int kDeltaKS = 8;     // lanes that share a column of the state
+constexpr int kDeltaKS = 8;     // lanes that share a column of the state in the kernels after the walk
+constexpr int kDeltaNC = 2;     // columns of the state a thread of the walk holds
 
 // KL: state values a thread holds, KS: threads to a column (dim <= KL KS).  qkv float32 [n, 2 G dim + H vdim]; beta_g float32 [n, 2 H].
 // PASS 0: a unit is a sequence (or, without the sequences' tables, a row): its tokens of the step in order, from and
@@ -175,7 +176,7 @@ __device__ __forceinline__ void delta_stage(float* dst, int stride, int rows, in
 template <int KS>
 __device__ __forceinline__ int scan_channel(int r, int part) { return (r >> 2) * (4 * KS) + part * 4 + (r & 3); }
 
-template <int KL, int KS, int PASS>
+template <int KL, int KS, int NC, int PASS>
 __global__ void __launch_bounds__(32 * KS)
 delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_g, float* __restrict__ state,
                   const int* __restrict__ token_pos, const int* __restrict__ token_seq,
@@ -184,12 +185,13 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
                   float* __restrict__ seg_state, float* __restrict__ seg_trans, float* __restrict__ q_run,
                   float* __restrict__ o_raw, int H, int G, int dim, int vdim) {
     constexpr int TT = kDeltaTile, DP = KL * KS, NT = 32 * KS;  // DP: dim rounded up, the tile's row
+    constexpr int CW = 32 * NC;                                  // columns of the state a CTA holds
     static_assert(NT >= TT && KL % 4 == 0, "a thread per token of a tile; channels in fours");
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;              // [TT][DP], zero past dim
     float* ks = qs + TT * DP;      // [TT][DP]
-    float* vs = ks + TT * DP;      // [TT][32]
-    float* bs = vs + TT * 32;      // [TT] beta
+    float* vs = ks + TT * DP;      // [TT][CW]
+    float* bs = vs + TT * CW;      // [TT] beta
     float* gs = bs + TT;           // [TT] decay
     float* kqs = gs + TT;          // [TT] k . q
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -213,24 +215,26 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
     }
     if (count <= 0) return;
     const int part = tid & (KS - 1);               // which share of the column
-    const int cg = tid / KS;                       // which of the CTA's 32 columns
-    const int value_tiles = (vdim + 31) / 32;
+    const int cg = tid / KS;                       // which NC of the CTA's columns
+    const int value_tiles = (vdim + CW - 1) / CW;
     const bool trans = PASS == 1 && (int)blockIdx.z >= value_tiles;
-    const int tile0 = (trans ? (int)blockIdx.z - value_tiles : (int)blockIdx.z) * 32;
-    const int col = tile0 + cg;                    // the column of the state
+    const int tile0 = (trans ? (int)blockIdx.z - value_tiles : (int)blockIdx.z) * CW;
+    const int col = tile0 + cg * NC;               // the first of the thread's columns of the state
     const int ncols = trans ? dim : vdim;
-    const bool live = col < ncols;
     const int kv = h / (H / G);
     const int cols = 2 * G * dim + H * vdim;
     float* S = PASS == 0 ? state + (((size_t)slot * H + h) * dim) * vdim
                : trans   ? seg_trans + (((size_t)unit * H + h) * dim) * dim
                          : seg_state + (((size_t)unit * H + h) * dim) * vdim;
-    float s[KL];
+    float s[NC][KL];
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
         const int d = scan_channel<KS>(r, part);
-        if (PASS == 0) s[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
-        else s[r] = (trans && live && d == col) ? 1.f : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            if (PASS == 0) s[c][r] = (col + c < ncols && d < dim) ? S[(size_t)d * vdim + col + c] : 0.f;
+            else s[c][r] = (trans && col + c < ncols && d == col + c) ? 1.f : 0.f;
+        }
     }
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int cnt = min(TT, count - t0);
@@ -239,7 +243,7 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
         delta_stage<DP, NT>(qs, DP, cnt, dim, [&](int i, int d) { return rows[(size_t)i * cols + (size_t)kv * dim + d]; });
         delta_stage<DP, NT>(ks, DP, cnt, dim,
                             [&](int i, int d) { return rows[(size_t)i * cols + (size_t)(G + kv) * dim + d]; });
-        delta_stage<32, NT>(vs, 32, cnt, 32, [&](int i, int c) {
+        delta_stage<CW, NT>(vs, CW, cnt, CW, [&](int i, int c) {
             return (!trans && tile0 + c < vdim) ? rows[(size_t)i * cols + 2 * G * dim + (size_t)h * vdim + tile0 + c] : 0.f;
         });
         if (tid < cnt) {
@@ -257,7 +261,14 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
         for (int i = 0; i < cnt; ++i) {
             const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * 4);
             const float4* k4 = reinterpret_cast<const float4*>(ks + i * DP + part * 4);
-            float sk[2] = {0.f, 0.f}, sq[2] = {0.f, 0.f};  // two chains each: a sum of KL terms is long
+            // a thread's NC columns share the token's q and k: one fetch feeds NC sums.  Two chains a sum where a
+            // thread has one column (a sum of KL terms is long); NC columns are chains enough
+            constexpr int CH = NC == 1 ? 2 : 1;
+            float sk[NC][CH], sq[NC][CH];
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int j = 0; j < CH; ++j) sk[c][j] = sq[c][j] = 0.f;
             float kr[KL];
 #pragma unroll
             for (int r4 = 0; r4 < KL / 4; ++r4) {
@@ -266,32 +277,41 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     kr[r4 * 4 + e] = kx[e];
-                    sk[e & 1] = fmaf(s[r4 * 4 + e], kx[e], sk[e & 1]);
-                    sq[e & 1] = fmaf(s[r4 * 4 + e], qx[e], sq[e & 1]);
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        sk[c][e % CH] = fmaf(s[c][r4 * 4 + e], kx[e], sk[c][e % CH]);
+                        sq[c][e % CH] = fmaf(s[c][r4 * 4 + e], qx[e], sq[c][e % CH]);
+                    }
                 }
             }
-            float sks = sk[0] + sk[1], sqs = sq[0] + sq[1];
+            const float g = gs[i], beta = bs[i], kq = kqs[i];
 #pragma unroll
-            for (int o = KS / 2; o > 0; o >>= 1) {
-                sks += __shfl_xor_sync(0xffffffffu, sks, o);
-                sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
-            }
-            // o = (g S + k u^T)^T q = g S^T q + u (k . q), with S the state before the token
-            const float g = gs[i];
-            const float u = bs[i] * (vs[i * 32 + cg] - g * sks);
+            for (int c = 0; c < NC; ++c) {
+                float sks = sk[c][0], sqs = sq[c][0];
+                if (CH == 2) { sks += sk[c][CH - 1]; sqs += sq[c][CH - 1]; }
 #pragma unroll
-            for (int r = 0; r < KL; ++r) s[r] = fmaf(kr[r], u, g * s[r]);
-            if (part == 0 && live) {
-                const float o = fmaf(u, kqs[i], g * sqs);
-                if (trans) q_run[((size_t)(first + t0 + i) * H + h) * dim + col] = o;
-                else o_raw[((size_t)(first + t0 + i) * H + h) * vdim + col] = o;
+                for (int o = KS / 2; o > 0; o >>= 1) {
+                    sks += __shfl_xor_sync(0xffffffffu, sks, o);
+                    sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
+                }
+                // o = (g S + k u^T)^T q = g S^T q + u (k . q), with S the state before the token
+                const float u = beta * (vs[i * CW + cg * NC + c] - g * sks);
+#pragma unroll
+                for (int r = 0; r < KL; ++r) s[c][r] = fmaf(kr[r], u, g * s[c][r]);
+                if (part == 0 && col + c < ncols) {
+                    const float o = fmaf(u, kq, g * sqs);
+                    if (trans) q_run[((size_t)(first + t0 + i) * H + h) * dim + col + c] = o;
+                    else o_raw[((size_t)(first + t0 + i) * H + h) * vdim + col + c] = o;
+                }
             }
         }
     }
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
         const int d = scan_channel<KS>(r, part);
-        if (live && d < dim) S[(size_t)d * ncols + col] = s[r];
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+            if (col + c < ncols && d < dim) S[(size_t)d * ncols + col + c] = s[c][r];
     }
 }
 
@@ -491,20 +511,22 @@ NNIS_API int nnis_delta_prep(const float* a, const float* conv_w, float* tail, c
 
 namespace nnis {
 
-template <int KL, int SKL, int SKS>
+template <int KL, int SKL, int SKS, int SNC>
 static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* state, const int* token_pos,
                                 const int* token_seq, const int* seq_slots, const int* seq_first_row,
                                 const int* seq_count, const int* segments, int n_segments,
                                 const int* seq_first_segment, int seg_len, float* seg_state, float* seg_trans,
                                 float* q_run, float* o_raw, int n_units, int H, int G, int dim, int vdim,
                                 cudaStream_t stream) {
-    const int value_tiles = (vdim + 31) / 32;
-    const size_t smem = ((size_t)2 * kDeltaTile * SKL * SKS + kDeltaTile * 32 + 3 * kDeltaTile) * sizeof(float);
+    const int value_tiles = (vdim + 31) / 32;  // of the kernels after the walk
+    constexpr int CW = 32 * SNC;               // the walk's own tiles
+    const int walk_tiles = (vdim + CW - 1) / CW;
+    const size_t smem = ((size_t)2 * kDeltaTile * SKL * SKS + kDeltaTile * CW + 3 * kDeltaTile) * sizeof(float);
     if (!segments)
-        return launch_dependent(delta_scan_kernel<SKL, SKS, 0>, dim3(n_units, H, value_tiles), 32 * SKS, smem, stream, qkv,
+        return launch_dependent(delta_scan_kernel<SKL, SKS, SNC, 0>, dim3(n_units, H, walk_tiles), 32 * SKS, smem, stream, qkv,
                                 beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments,
                                 seg_len, seg_state, seg_trans, q_run, o_raw, H, G, dim, vdim);
-    cudaError_t e = launch_dependent(delta_scan_kernel<SKL, SKS, 1>, dim3(n_segments, H, value_tiles + (dim + 31) / 32),
+    cudaError_t e = launch_dependent(delta_scan_kernel<SKL, SKS, SNC, 1>, dim3(n_segments, H, walk_tiles + (dim + CW - 1) / CW),
                                      32 * SKS, smem, stream, qkv, beta_g, state, token_pos, token_seq, seq_slots,
                                      seq_first_row, seq_count, segments, seg_len, seg_state, seg_trans, q_run, o_raw,
                                      H, G, dim, vdim);
@@ -544,14 +566,14 @@ NNIS_API int nnis_delta_scan(const float* qkv, const float* beta_g, float* state
         return NNIS_ERR_ARGUMENT;
     if (dim > 256 || H > 65535 || (vdim + 31) / 32 + (dim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
     cudaError_t e;
-#define NNIS_DELTA_CASE(KL, SKL, SKS) \
-    e = delta_passes<KL, SKL, SKS>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
+#define NNIS_DELTA_CASE(KL, SKL, SKS, SNC) \
+    e = delta_passes<KL, SKL, SKS, SNC>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
                          n_segments, seq_first_segment, seg_len, seg_state, seg_trans, q_run, o_raw, n_units, H, G, \
                          dim, vdim, stream)
-    if (dim <= 32) NNIS_DELTA_CASE(4, 32, 1);
-    else if (dim <= 64) NNIS_DELTA_CASE(8, 32, 2);
-    else if (dim <= 128) NNIS_DELTA_CASE(16, 32, 4);
-    else NNIS_DELTA_CASE(32, 32, 8);
+    if (dim <= 32) NNIS_DELTA_CASE(4, 32, 1, kDeltaNC);
+    else if (dim <= 64) NNIS_DELTA_CASE(8, 32, 2, kDeltaNC);
+    else if (dim <= 128) NNIS_DELTA_CASE(16, 32, 4, kDeltaNC);
+    else NNIS_DELTA_CASE(32, 32, 8, kDeltaNC);
 #undef NNIS_DELTA_CASE
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }

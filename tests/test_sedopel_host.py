@@ -35,6 +35,9 @@ def test_configuration_round_trip_and_spec():
     assert right.kind == "retention" and right["decay"] == (0.9, 0.999, 0.5) and right["activation"] == "silu"
     assert right["norm"] == "joined" and right["gate"] == "sigmoid" and right["key_scale"] == 1.0
     assert pair["weight"] == 0.5
+    one = copy.deepcopy(MIXED)
+    one["layers"][1]["mixer"]["right"]["decay"] = 0.75  # one number stands for every head
+    assert config_from_dict(one).to_spec().layers[1].part("mixer")["right"]["decay"] == (0.75, 0.75, 0.75)
     delta = spec.layers[0].part("mixer")
     assert delta["taps"] == 4 and delta["kv_heads"] == 2 and delta["unit_eps"] == 1e-6 and delta["eps"] == 1e-5
     assert spec.layers[0].part("ffn")["activation"] == "gelu" and spec.layers[0].part("ffn")["intermediate_size"] == 72
