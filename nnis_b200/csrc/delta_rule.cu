@@ -316,11 +316,15 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ beta_
 }
 
 // Between the runs' own walk and the product that finishes their outputs: a CTA per (sequence, head, 32 value
-// columns) walks the sequence's runs in order with the state in registers (the scan's layout).  seg_state[run]
-// (what the run adds) becomes the state before the run; the state after it is P_run S_before + S_run, a product
-// with the run's transition taken 64 of its columns at a time through shared memory; the slot's state becomes the
-// state after the last run.
-constexpr int kDeltaPrefixCols = 64;
+// columns) walks the sequence's runs in order.  seg_state[run] (what the run adds) becomes the state before the
+// run; the state after it is P_run S_before + S_run, a product with the run's transition taken 32 of its columns at
+// a time through shared memory.  A lane owns a column, warp w its rows w, w + 8, ...: a warp reads the transition's
+// row 16 bytes a load from ONE address (a broadcast), and the carried column lies along a row of shared memory to be
+// read the same way, so 64 multiply-adds take 17 loads of which 16 cost one trip.  The next 32 columns of the
+// transition (the next run's first, at a run's end) are fetched into registers while the current ones are
+// multiplied.  The slot's state becomes the state after the last run.
+constexpr int kDeltaPrefixCols = 32;   // columns of the transition a trip
+constexpr int kDeltaApplyNC = 4;       // value columns a thread of the last product holds
 
 template <int KL>
 __global__ void __launch_bounds__(256)
@@ -328,48 +332,65 @@ delta_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots
                     const int* __restrict__ seq_first_segment, float* __restrict__ seg_state,
                     const float* __restrict__ seg_trans, int H, int dim, int vdim) {
     constexpr int KS = kDeltaKS, EC = kDeltaPrefixCols, DP = KL * KS;
+    constexpr int CS = DP + 4, PS = EC + 4;  // row strides: 16-byte rows, neighbours four banks apart
+    static_assert(KS == 8 && EC == 32, "eight warps of 32 lanes: a warp a row of the trip, a lane a column");
     extern __shared__ __align__(16) float smem[];
-    float* cs = smem;             // [DP][32]: the carried state's columns of this tile
-    float* ps = cs + DP * 32;     // [DP][EC + 1]: EC columns of the transition, zero past dim
-    const int tid = threadIdx.x, part = tid & (KS - 1), cg = tid >> 3;
-    for (int i = tid; i < DP * (EC + 1); i += 256) ps[i] = 0.f;
+    float* cs = smem;             // [32][CS]: the carried state, a column of it a row
+    float* ps = cs + 32 * CS;     // [DP][PS]: EC columns of the transition, zero past dim
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     pdl_wait();
     pdl_launch_dependents();
     const int seq = blockIdx.x, h = blockIdx.y;
-    const int col = blockIdx.z * 32 + cg;
+    const int col = blockIdx.z * 32 + lane;
     const bool live = col < vdim;
     float* S = state + (((size_t)seq_slots[seq] * H + h) * dim) * vdim;
-    float carry[KL];
+    float carry[KL], pre[KL];
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
-        const int d = delta_channel(r, part);
+        const int d = w + KS * r;
         carry[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
     }
-    const int last = seq_first_segment[seq + 1];
-    for (int run = seq_first_segment[seq]; run < last; ++run) {
-        float* local = seg_state + (((size_t)run * H + h) * dim) * vdim;
+    // row w + 8 k, column e0 + lane of a run's transition: the thread's share of a trip
+    auto fetch = [&](int run, int e0) {
         const float* P = seg_trans + (((size_t)run * H + h) * dim) * dim;
+#pragma unroll
+        for (int k = 0; k < KL; ++k) {
+            const int d = w + KS * k;
+            pre[k] = (d < dim && e0 + lane < dim) ? P[(size_t)d * dim + e0 + lane] : 0.f;
+        }
+    };
+    const int first_run = seq_first_segment[seq], last = seq_first_segment[seq + 1];
+    if (first_run < last) fetch(first_run, 0);
+    for (int run = first_run; run < last; ++run) {
+        float* local = seg_state + (((size_t)run * H + h) * dim) * vdim;
         float acc[KL];
 #pragma unroll
         for (int r = 0; r < KL; ++r) {
-            const int d = delta_channel(r, part);
+            const int d = w + KS * r;
             acc[r] = (live && d < dim) ? local[(size_t)d * vdim + col] : 0.f;
         }
 #pragma unroll
         for (int r = 0; r < KL; ++r) {
-            const int d = delta_channel(r, part);
+            const int d = w + KS * r;
             if (live && d < dim) local[(size_t)d * vdim + col] = carry[r];
-            cs[d * 32 + cg] = carry[r];
+            cs[lane * CS + d] = carry[r];
         }
         for (int e0 = 0; e0 < dim; e0 += EC) {
-            const int en = min(EC, dim - e0);
-            __syncthreads();  // cs is whole; the chunk before is read
-            delta_stage<EC, 256>(ps, EC + 1, dim, en, [&](int d, int ee) { return P[(size_t)d * dim + e0 + ee]; });
-            __syncthreads();
-            for (int ee = 0; ee < en; ++ee) {
-                const float c = cs[(e0 + ee) * 32 + cg];
+            __syncthreads();  // cs is whole; the trip before is read
 #pragma unroll
-                for (int r = 0; r < KL; ++r) acc[r] = fmaf(ps[delta_channel(r, part) * (EC + 1) + ee], c, acc[r]);
+            for (int k = 0; k < KL; ++k) ps[(w + KS * k) * PS + lane] = pre[k];
+            if (e0 + EC < dim) fetch(run, e0 + EC);
+            else if (run + 1 < last) fetch(run + 1, 0);
+            __syncthreads();
+            const float* crow = cs + lane * CS + e0;  // e0 + EC <= DP; past dim both factors are zero
+#pragma unroll
+            for (int ee = 0; ee < EC; ee += 4) {
+                const float4 c = *reinterpret_cast<const float4*>(crow + ee);
+#pragma unroll
+                for (int r = 0; r < KL; ++r) {
+                    const float4 p = *reinterpret_cast<const float4*>(ps + (w + KS * r) * PS + ee);
+                    acc[r] = fmaf(p.w, c.w, fmaf(p.z, c.z, fmaf(p.y, c.y, fmaf(p.x, c.x, acc[r]))));
+                }
             }
         }
         __syncthreads();  // cs is read before the next run writes it
@@ -378,25 +399,26 @@ delta_prefix_kernel(float* __restrict__ state, const int* __restrict__ seq_slots
     }
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
-        const int d = delta_channel(r, part);
+        const int d = w + KS * r;
         if (live && d < dim) S[(size_t)d * vdim + col] = carry[r];
     }
 }
 
 // o_raw[t, h, :] += S_before(run of t)^T q_run[t, h, :]: what the tokens before a run contribute to its outputs.
-// A CTA per (run, head, 32 value columns) holds its tile of S_before in registers (the scan's layout); the sums of
-// 16 tokens go through shared memory so that a row's 32 values are added to o_raw side by side.
+// A CTA per (run, head, 128 value columns) holds its tile of S_before in registers: eight lanes share four
+// neighbouring columns (the scan's layout of channels), so one fetch of a token's q feeds four sums; the sums of 16
+// tokens go through shared memory so that a row's values are added to o_raw side by side.
 template <int KL>
 __global__ void __launch_bounds__(256)
 delta_apply_kernel(const float* __restrict__ q_run, const float* __restrict__ seg_state,
                    const int* __restrict__ seq_first_row, const int* __restrict__ seq_count,
                    const int* __restrict__ segments, int seg_len, float* __restrict__ o_raw, int H, int dim,
                    int vdim) {
-    constexpr int KS = kDeltaKS, TT = kDeltaTile, DP = KL * KS;
+    constexpr int KS = kDeltaKS, TT = kDeltaTile, DP = KL * KS, NC = kDeltaApplyNC, CW = 32 * NC;
     extern __shared__ __align__(16) float smem[];
     float* qs = smem;            // [TT][DP], zero past dim
-    float* os = qs + TT * DP;    // [TT][32]
-    const int tid = threadIdx.x, part = tid & (KS - 1);
+    float* os = qs + TT * DP;    // [TT][CW]
+    const int tid = threadIdx.x, part = tid & (KS - 1), cg = tid >> 3;
     for (int i = tid; i < TT * DP; i += 256) qs[i] = 0.f;
     pdl_wait();
     pdl_launch_dependents();
@@ -405,40 +427,48 @@ delta_apply_kernel(const float* __restrict__ q_run, const float* __restrict__ se
     const int first = seq_first_row[seq] + t_first;
     const int count = min(seg_len, seq_count[seq] - t_first);
     if (count <= 0) return;
-    const int tile0 = blockIdx.z * 32;
-    const int col = tile0 + (tid >> 3);
-    const bool live = col < vdim;
+    const int tile0 = blockIdx.z * CW;
+    const int col = tile0 + cg * NC;  // the first of the thread's columns
     const float* S = seg_state + (((size_t)unit * H + h) * dim) * vdim;
-    float s[KL];
+    float s[NC][KL];
 #pragma unroll
     for (int r = 0; r < KL; ++r) {
         const int d = delta_channel(r, part);
-        s[r] = (live && d < dim) ? S[(size_t)d * vdim + col] : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) s[c][r] = (col + c < vdim && d < dim) ? S[(size_t)d * vdim + col + c] : 0.f;
     }
     for (int t0 = 0; t0 < count; t0 += TT) {
         const int cnt = min(TT, count - t0);
         __syncthreads();
         delta_stage<DP, 256>(qs, DP, cnt, dim, [&](int i, int d) { return q_run[((size_t)(first + t0 + i) * H + h) * dim + d]; });
         __syncthreads();
-#pragma unroll 4
+#pragma unroll 2
         for (int i = 0; i < cnt; ++i) {
             const float4* q4 = reinterpret_cast<const float4*>(qs + i * DP + part * 4);
-            float acc = 0.f;
+            float acc[NC];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[c] = 0.f;
 #pragma unroll
             for (int r4 = 0; r4 < KL / 4; ++r4) {
                 const float4 qq = q4[r4 * 8];
-                acc = fmaf(s[r4 * 4], qq.x, acc);
-                acc = fmaf(s[r4 * 4 + 1], qq.y, acc);
-                acc = fmaf(s[r4 * 4 + 2], qq.z, acc);
-                acc = fmaf(s[r4 * 4 + 3], qq.w, acc);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    acc[c] = fmaf(s[c][r4 * 4], qq.x, acc[c]);
+                    acc[c] = fmaf(s[c][r4 * 4 + 1], qq.y, acc[c]);
+                    acc[c] = fmaf(s[c][r4 * 4 + 2], qq.z, acc[c]);
+                    acc[c] = fmaf(s[c][r4 * 4 + 3], qq.w, acc[c]);
+                }
             }
 #pragma unroll
-            for (int o = KS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (part == 0) os[i * 32 + (tid >> 3)] = acc;
+            for (int c = 0; c < NC; ++c) {
+#pragma unroll
+                for (int o = KS / 2; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+            }
+            if (part == 0) *reinterpret_cast<float4*>(os + i * CW + cg * NC) = make_float4(acc[0], acc[1], acc[2], acc[3]);
         }
         __syncthreads();
-        for (int it = tid; it < cnt * 32; it += 256) {
-            const int i = it >> 5, c = tile0 + (it & 31);
+        for (int it = tid; it < cnt * CW; it += 256) {
+            const int i = it / CW, c = tile0 + it % CW;
             if (c < vdim) o_raw[((size_t)(first + t0 + i) * H + h) * vdim + c] += os[it];
         }
     }
@@ -518,7 +548,6 @@ static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* st
                                 const int* seq_first_segment, int seg_len, float* seg_state, float* seg_trans,
                                 float* q_run, float* o_raw, int n_units, int H, int G, int dim, int vdim,
                                 cudaStream_t stream) {
-    const int value_tiles = (vdim + 31) / 32;  // of the kernels after the walk
     constexpr int CW = 32 * SNC;               // the walk's own tiles
     const int walk_tiles = (vdim + CW - 1) / CW;
     const size_t smem = ((size_t)2 * kDeltaTile * SKL * SKS + kDeltaTile * CW + 3 * kDeltaTile) * sizeof(float);
@@ -531,18 +560,21 @@ static cudaError_t delta_passes(const float* qkv, const float* beta_g, float* st
                                      seq_first_row, seq_count, segments, seg_len, seg_state, seg_trans, q_run, o_raw,
                                      H, G, dim, vdim);
     if (e != cudaSuccess) return e;
-    const size_t prefix_smem = (size_t)KL * kDeltaKS * (32 + kDeltaPrefixCols + 1) * sizeof(float);
+    const size_t prefix_smem = ((size_t)32 * (KL * kDeltaKS + 4) +
+                                (size_t)KL * kDeltaKS * (kDeltaPrefixCols + 4)) * sizeof(float);
     if (prefix_smem > 48 * 1024) {
         e = cudaFuncSetAttribute(delta_prefix_kernel<KL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)prefix_smem);
         if (e != cudaSuccess) return e;
     }
-    e = launch_dependent(delta_prefix_kernel<KL>, dim3(n_units, H, value_tiles), 256, prefix_smem, stream, state,
+    e = launch_dependent(delta_prefix_kernel<KL>, dim3(n_units, H, (vdim + 31) / 32), 256, prefix_smem, stream, state,
                          seq_slots, seq_first_segment, seg_state, (const float*)seg_trans, H, dim, vdim);
     if (e != cudaSuccess) return e;
-    return launch_dependent(delta_apply_kernel<KL>, dim3(n_segments, H, value_tiles), 256,
-                            (size_t)kDeltaTile * (KL * kDeltaKS + 32) * sizeof(float), stream, (const float*)q_run,
-                            (const float*)seg_state, seq_first_row, seq_count, segments, seg_len, o_raw, H, dim, vdim);
+    constexpr int apply_cols = 32 * kDeltaApplyNC;
+    return launch_dependent(delta_apply_kernel<KL>, dim3(n_segments, H, (vdim + apply_cols - 1) / apply_cols), 256,
+                            (size_t)kDeltaTile * (KL * kDeltaKS + apply_cols) * sizeof(float), stream,
+                            (const float*)q_run, (const float*)seg_state, seq_first_row, seq_count, segments, seg_len,
+                            o_raw, H, dim, vdim);
 }
 
 }  // namespace nnis
@@ -564,7 +596,7 @@ NNIS_API int nnis_delta_scan(const float* qkv, const float* beta_g, float* state
     if (segments && (!seq_first_row || !seq_first_segment || n_segments <= 0 || seg_len <= 0 || !seg_state ||
                      !seg_trans || !q_run))
         return NNIS_ERR_ARGUMENT;
-    if (dim > 256 || H > 65535 || (vdim + 31) / 32 + (dim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
+    if (dim > 256 || H > 65535 || (vdim + 31) / 32 > 65535) return NNIS_ERR_UNSUPPORTED;
     cudaError_t e;
 #define NNIS_DELTA_CASE(KL, SKL, SKS, SNC) \
     e = delta_passes<KL, SKL, SKS, SNC>(qkv, beta_g, state, token_pos, token_seq, seq_slots, seq_first_row, seq_count, segments, \
