@@ -82,6 +82,92 @@ norm_scale_add_kernel(float* __restrict__ branch, const float* __restrict__ w,
     }
 }
 
+// One to four values of a row at a time: four where rows start on 16-byte borders.
+__device__ __forceinline__ void row_load(const float* p, int v, float* x) {
+    if (v == 4) { const float4 t = load4(p); x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w; }
+    else x[0] = p[0];
+}
+__device__ __forceinline__ void row_store(float* p, int v, const float* x) {
+    if (v == 4) store4(p, make_float4(x[0], x[1], x[2], x[3]));
+    else p[0] = x[0];
+}
+template <typename T>
+__device__ __forceinline__ void row_store(T* p, int v, const float* x) {
+    if (v == 4) store4(p, make_float4(x[0], x[1], x[2], x[3]));
+    else p[0] = from_float<T>(x[0]);
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();  // (the sums of a reduction before are read)
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) total += red[k];
+    return total;
+}
+
+// What closes a sub-layer of a block with a norm on either side, in one pass over the row (a CTA of 256 threads a
+// row; a thread meets the same values in every loop, so only the sums need barriers):
+//   hidden += rms(branch) * w, and branch is left zero;
+//   with terms > 0 the new row is kept as history[terms - 1] and replaced by sum_j mix_w[j] history[j];
+//   with w_next the row's RMS norm times w_next is written to `normed` in the operand dtype (the norm that reads
+//   the row next: the one before the block's feed-forward, or the next block's first).
+template <typename T>
+__global__ void __launch_bounds__(256)
+sandwich_close_kernel(float* __restrict__ branch, const float* __restrict__ w, float eps, float* __restrict__ hidden,
+                      float* __restrict__ history, const float* __restrict__ mix_w, int terms, size_t plane,
+                      const float* __restrict__ w_next, float eps_next, T* __restrict__ normed, int width) {
+    __shared__ float red[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    float* b = branch + row * width;
+    float* h = hidden + row * width;
+    const int V = (width & 3) == 0 ? 4 : 1;
+    float ss = 0.f;
+    for (int i = threadIdx.x * V; i < width; i += 256 * V) {
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        row_load(b + i, V, x);
+        ss = fmaf(x[0], x[0], fmaf(x[1], x[1], fmaf(x[2], x[2], fmaf(x[3], x[3], ss))));
+    }
+    const float s = 1.0f / sqrtf(block_sum_256(ss, red) / (float)width + eps);
+    const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+    float ss2 = 0.f;
+    for (int i = threadIdx.x * V; i < width; i += 256 * V) {
+        float bv[4], wv[4], v[4] = {0.f, 0.f, 0.f, 0.f};
+        row_load(b + i, V, bv);
+        row_load(w + i, V, wv);
+        row_load(h + i, V, v);
+        for (int e = 0; e < V; ++e) v[e] = fmaf(bv[e] * s, wv[e], v[e]);
+        row_store(b + i, V, zero);
+        if (terms > 0) {
+            row_store(history + (size_t)(terms - 1) * plane + row * width + i, V, v);
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j + 1 < terms; ++j) {
+                float x[4];
+                row_load(history + (size_t)j * plane + row * width + i, V, x);
+                const float wj = mix_w[j];
+                for (int e = 0; e < V; ++e) sum[e] = fmaf(wj, x[e], sum[e]);
+            }
+            const float wl = mix_w[terms - 1];
+            for (int e = 0; e < V; ++e) v[e] = fmaf(wl, v[e], sum[e]);
+        }
+        row_store(h + i, V, v);
+        ss2 = fmaf(v[0], v[0], fmaf(v[1], v[1], fmaf(v[2], v[2], fmaf(v[3], v[3], ss2))));
+    }
+    if (!w_next) return;
+    const float s2 = 1.0f / sqrtf(block_sum_256(ss2, red) * (1.0f / (float)width) + eps_next);
+    for (int i = threadIdx.x * V; i < width; i += 256 * V) {
+        float v[4], wv[4];
+        row_load(h + i, V, v);  // the thread's own values
+        row_load(w_next + i, V, wv);
+        for (int e = 0; e < V; ++e) v[e] = (v[e] * s2) * wv[e];
+        row_store(normed + row * width + i, V, v);
+    }
+}
+
 template <typename T>
 __global__ void glu_clamp_kernel(const float* __restrict__ gate_up, T* __restrict__ out, size_t n_rows,
                                  int inter, float limit, float alpha) {
@@ -191,6 +277,27 @@ NNIS_API int nnis_norm_scale_add(float* branch, const float* w, float* hidden, v
     else if (out_dtype == NNIS_DTYPE_BF16)
         e = launch_dependent(norm_scale_add_kernel<bf16>, (unsigned)n_rows, 256, 0, stream, branch, w, hidden,
                              (bf16*)out, width, eps, mult, clear);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+// history [at least terms, n_rows, width] and mix_w [terms] with terms > 0, else unused; w_next and normed
+// (operand dtype) together or neither
+NNIS_API int nnis_sandwich_close(float* branch, const float* w, float eps, float* hidden, float* history,
+                                 const float* mix_w, int terms, const float* w_next, float eps_next, void* normed,
+                                 int out_dtype, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0 || !(eps > 0.f) || !branch || !w || !hidden || terms < 0 ||
+        (terms > 0 && (!history || !mix_w)) || (!w_next != !normed) || (w_next && !(eps_next > 0.f)))
+        return NNIS_ERR_ARGUMENT;
+    const size_t plane = (size_t)n_rows * width;
+    cudaError_t e;
+    if (out_dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(sandwich_close_kernel<float>, (unsigned)n_rows, 256, 0, stream, branch, w, eps, hidden,
+                             history, mix_w, terms, plane, w_next, eps_next, (float*)normed, width);
+    else if (out_dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(sandwich_close_kernel<bf16>, (unsigned)n_rows, 256, 0, stream, branch, w, eps, hidden,
+                             history, mix_w, terms, plane, w_next, eps_next, (bf16*)normed, width);
     else
         return NNIS_ERR_UNSUPPORTED;
     return e == cudaSuccess ? NNIS_OK : (int)e;

@@ -1338,6 +1338,36 @@ def norm_scale_add(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult:
            "norm_scale_add")
 
 
+def sandwich_close(branch: torch.Tensor, weight: torch.Tensor, eps: float, hidden: torch.Tensor,
+                   history: Optional[torch.Tensor] = None, mix_weights: Optional[torch.Tensor] = None, terms: int = 0,
+                   next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
+                   normed: Optional[torch.Tensor] = None) -> None:
+    """hidden += rmsnorm(branch) * weight and branch is zero afterwards (float32 [n, width]).  With
+    ``terms`` > 0 the new rows are kept as history[terms - 1] and hidden becomes sum over j < terms of
+    mix_weights[j] * history[j] (history float32 [at least terms, n, width]).  With ``next_weight``
+    the RMS norm of the rows that hidden then holds, times next_weight, is written to ``normed``
+    ([n, width], its own dtype)."""
+    _cuda(branch, weight, hidden, history, mix_weights, next_weight, normed)
+    n, width = hidden.shape
+    _need(branch.dtype == hidden.dtype == weight.dtype == torch.float32 and tuple(branch.shape) == (n, width)
+          and weight.numel() == width and hidden.is_contiguous() and branch.is_contiguous(),
+          "sandwich_close: float32 [n, width] rows and [width] weights")
+    if terms > 0:
+        _need(history is not None and mix_weights is not None and history.dtype == mix_weights.dtype == torch.float32
+              and history.dim() == 3 and history.shape[0] >= terms and tuple(history.shape[1:]) == (n, width)
+              and history.is_contiguous() and mix_weights.numel() == terms,
+              "sandwich_close: history [terms, n, width] and a weight per term")
+    _need((next_weight is None) == (normed is None), "sandwich_close: next_weight and normed go together")
+    if normed is not None:
+        _need(next_weight.dtype == torch.float32 and next_weight.numel() == width and tuple(normed.shape) == (n, width)
+              and normed.is_contiguous(), "sandwich_close: normed [n, width], float32 weights")
+    _check(_lib().nnis_sandwich_close(_ptr(branch), _ptr(weight), ctypes.c_float(eps), _ptr(hidden),
+                                      _ptr(history) if terms > 0 else None, _ptr(mix_weights) if terms > 0 else None,
+                                      int(terms), _ptr(next_weight), ctypes.c_float(next_eps), _ptr(normed),
+                                      code_of(normed.dtype) if normed is not None else F32, n, width, _stream()),
+           "sandwich_close")
+
+
 def glu_clamp(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
     """out = g' * sigmoid(alpha * g') * (u' + 1) with g' = min(gate, limit) and u' = up clamped
     to [-limit, limit]; gate_up float32 [n, 2I] (gate columns first)."""

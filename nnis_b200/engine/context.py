@@ -70,6 +70,11 @@ class StepContext:
     # (and cleared) by the block that runs next.
     hidden_copy: object = None
     copy_turn: int = 0  # which of that block's two buffers was written last
+    # ``next_block``: set by the model while a block runs, the block that runs after it (None after
+    # the last).  ``normed_rows``: (norm, rows) left by a block that applied the next block's first
+    # norm in the kernel that wrote the stream last; taken (and cleared) by the block that owns the norm.
+    next_block: object = None
+    normed_rows: object = None
 
     def take_shared_norm(self, norm):
         """What the part before left of ``norm``'s work, or None; nothing is kept."""

@@ -117,15 +117,16 @@ class DecoderModel:
     def _run_blocks(self, ctx) -> torch.Tensor:
         hidden = ctx.workspace.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx.tokens, hidden, self.status)
-        ctx.hidden_copy = None  # (a context may run more than one step: nothing of the last one counts)
+        ctx.hidden_copy = ctx.normed_rows = None  # (a context may run more than one step: nothing of the last one counts)
         schedule = self.spec.schedule
         for i, entry in enumerate(schedule):
             # a block may begin the first norm of the block after it, if that one takes it
             ask = getattr(self.blocks[schedule[i + 1].layer], "first_shared_norm", None) \
                 if i + 1 < len(schedule) else None
             ctx.next_norm = ask(ctx, ctx.n_tokens) if ask is not None else None
+            ctx.next_block = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
             self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
-        ctx.next_norm = ctx.shared_norm = ctx.hidden_copy = None
+        ctx.next_norm = ctx.next_block = ctx.shared_norm = ctx.hidden_copy = ctx.normed_rows = None
         return hidden
 
     def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:

@@ -303,6 +303,16 @@ class SandwichBlock(Block):
         if self.mix_name:
             self.mix_weights = tensors[self.mix_name]
 
+    def _close(self, branch, post, hidden, history, follower, normed) -> bool:
+        """The kernel that ends a sub-layer: the norm of its output into the stream, the depth mix
+        if ``history`` is given, and the norm ``follower`` of the rows the stream then holds, if it is
+        an RMS norm.  True if ``normed`` was written."""
+        fused = follower is not None and getattr(follower, "kind", None) == "rmsnorm"
+        ops.sandwich_close(branch, post.weight, post.eps, hidden, history, self.mix_weights if history is not None else None,
+                           self.mix_terms if history is not None else 0,
+                           follower.weight if fused else None, follower.eps if fused else 0.0, normed if fused else None)
+        return fused
+
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
         ws = ctx.workspace
@@ -316,18 +326,23 @@ class SandwichBlock(Block):
         branch = ws.kept_zero("branch_out", (n, width), torch.float32)
         if not ctx.decode:
             branch.zero_()
-        self.mixer_norm.forward(hidden, normed)
+        begun, ctx.normed_rows = ctx.normed_rows, None
+        if begun is None or begun[0] is not self.mixer_norm or begun[1].data_ptr() != normed.data_ptr():
+            self.mixer_norm.forward(hidden, normed)
         self.mixer.forward(normed, ctx, branch, cache)
-        ops.norm_scale_add(branch, self.mixer_post.weight, self.mixer_post.eps, 1.0, hidden, clear=True)
-        if self.ffn is not None:
+        # the block after this one, if it is of this arrangement, finds its first norm done
+        after = ctx.next_block.mixer_norm if isinstance(ctx.next_block, SandwichBlock) else None
+        if self.ffn is None:
+            if self._close(branch, self.mixer_post, hidden, history, after, normed):
+                ctx.normed_rows = (after, normed)
+            return
+        if not self._close(branch, self.mixer_post, hidden, None, self.ffn_norm, normed):
             self.ffn_norm.forward(hidden, normed)
-            self.ffn.forward(normed, ctx, branch)
-            ops.norm_scale_add(branch, self.ffn_post.weight, self.ffn_post.eps, 1.0, hidden, clear=True)
-        if history is not None:
-            ops.depth_mix(hidden, history, self.mix_weights, self.mix_terms)
+        self.ffn.forward(normed, ctx, branch)
+        if self._close(branch, self.ffn_post, hidden, history, after, normed):
+            ctx.normed_rows = (after, normed)
 
 
-BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("branch_norm", BranchNormBlock)
 BLOCKS.register("parallel", ParallelBlock)

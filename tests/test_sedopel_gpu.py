@@ -91,6 +91,41 @@ def test_depth_mix_keeps_every_result_and_weights_them():
             assert torch.allclose(hidden.cpu().double(), want, atol=1e-5, rtol=1e-5)
 
 
+def test_closing_a_sub_layer_norms_adds_mixes_and_norms_again():
+    """The kernel that ends a sub-layer, in each of its forms: the norm of the branch added to the
+    stream (and the branch zero again), with and without the depth mix, with and without the norm
+    that reads the rows next, in both operand dtypes and for widths that are no multiples of four."""
+    from nnis_b200.csrc import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(5)
+
+    def rms(x, w, eps):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+
+    for n, width, most in ((5, 76, 4), (2, 7, 3), (9, 1000, 5), (3, 2048, 2)):
+        for terms in (0, 2, most):
+            for follower in (None, torch.float32, torch.bfloat16):
+                branch, stream = torch.randn(n, width, generator=g) * 3, torch.randn(n, width, generator=g)
+                w, w_next = torch.rand(width, generator=g) + 0.5, torch.rand(width, generator=g) + 0.5
+                kept, mix = torch.randn(most, n, width, generator=g), torch.randn(max(terms, 1), generator=g)
+                b, h, hist = branch.to(dev), stream.to(dev), kept.to(dev).clone()
+                normed = torch.full((n, width), 7.0, dtype=follower, device=dev) if follower else None
+                ops.sandwich_close(b, w.to(dev), 1e-5, h, hist if terms else None, mix.to(dev) if terms else None, terms,
+                                   w_next.to(dev) if follower else None, 1e-6 if follower else 0.0, normed)
+                result = stream.double() + rms(branch.double(), w.double(), 1e-5)
+                want = result
+                if terms:
+                    want = mix[terms - 1].double() * result + sum(mix[j].double() * kept[j].double() for j in range(terms - 1))
+                    assert torch.allclose(hist[terms - 1].cpu().double(), result, atol=1e-5, rtol=1e-5)
+                    assert torch.equal(hist[:terms - 1].cpu(), kept[:terms - 1]) and torch.equal(hist[terms:].cpu(), kept[terms:])
+                assert not b.any()
+                assert torch.allclose(h.cpu().double(), want, atol=2e-5, rtol=1e-5)
+                if follower:
+                    again = rms(h.cpu().double(), w_next.double(), 1e-6)
+                    tol = 1e-5 if follower == torch.float32 else 1e-2
+                    assert torch.allclose(normed.cpu().double(), again, atol=tol, rtol=tol)
+
+
 def test_gelu_rows_in_both_forms():
     from nnis_b200.csrc import ops
     dev = torch.device("cuda:0")
