@@ -343,6 +343,7 @@ class SandwichBlock(Block):
             ctx.normed_rows = (after, normed)
 
 
+BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("sandwich", SandwichBlock)
 BLOCKS.register("branch_norm", BranchNormBlock)
 BLOCKS.register("parallel", ParallelBlock)
