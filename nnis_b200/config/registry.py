@@ -17,6 +17,7 @@ from typing import Any, Dict, Mapping, Type
 from .llama import ConfigError, LlamaConfig
 from .nafezen import NafezenConfig
 from .sedopel import SedopelConfig
+from .selovik import SelovikConfig
 from .tazadra import TazadraConfig
 from .spec import ModelSpec
 
@@ -85,3 +86,4 @@ register_architecture(LlamaConfig.architecture, LlamaConfig)
 register_architecture(NafezenConfig.architecture, NafezenConfig)
 register_architecture(TazadraConfig.architecture, TazadraConfig)
 register_architecture(SedopelConfig.architecture, SedopelConfig)
+register_architecture(SelovikConfig.architecture, SelovikConfig)

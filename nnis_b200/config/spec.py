@@ -12,7 +12,11 @@ no part and no engine file names an architecture.  The spec is plain data:
   model may differ in every part and in how many they have;
 * ``schedule`` is the order in which layers run.  An entry may name a layer a
   second time (its weights are shared, its cache is its own), and
-  ``cache_of`` lets an entry read the cache that an earlier entry wrote.
+  ``cache_of`` lets an entry read the cache that an earlier entry wrote.  An entry
+  may also say what is added to the stream before its layer runs (``enter``): the
+  embedding output once more, and a row of a named tensor; a run of layers that is
+  passed through several times is a schedule that names its layers once per pass,
+  the first entry of every pass with its ``enter``.
 
 NNIS keeps the same facts as a capability record next to a fixed decoder
 (crates/nnis-model/src/decoder_capabilities.rs:8-75); here they drive the build.
@@ -54,11 +58,24 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class StreamEnter:
+    """What is added to the residual stream right before a schedule entry's layer runs:
+    the embedding output (the stream as it was before the first layer) if ``embedding``,
+    and row ``row`` of the float32 tensor ``tensor`` ([rows, width]) if it is named."""
+    embedding: bool = False
+    tensor: Optional[str] = None
+    rows: int = 0
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """Run ``layer``; read the cache of schedule entry ``cache_of`` instead of
-    writing one of its own when that is set (it must come earlier)."""
+    writing one of its own when that is set (it must come earlier); ``enter``: what
+    the stream takes up before the layer."""
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[StreamEnter] = None
 
 
 @dataclass(frozen=True)
@@ -91,6 +108,9 @@ class ModelSpec:
                 if self.schedule[entry.cache_of].cache_of is not None:
                     raise ValueError(f"schedule[{i}].cache_of={entry.cache_of} names an entry "
                                      f"that owns no cache itself")
+            if entry.enter is not None and entry.enter.tensor is not None \
+                    and not 0 <= entry.enter.row < entry.enter.rows:
+                raise ValueError(f"schedule[{i}].enter names row {entry.enter.row} of {entry.enter.rows}")
         for t in self.stop_token_ids:
             if not 0 <= t < self.vocab_size:
                 raise ValueError(f"stop token {t} is outside the vocabulary of {self.vocab_size}")

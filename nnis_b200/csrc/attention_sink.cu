@@ -12,7 +12,10 @@
 //                   value i with value i + rot / 2), then optionally an RMS norm of every q and k head
 //                   by itself (no weight, after the rotation), optionally a number per query head that
 //                   multiplies its q (a temperature of the scores), and `gate_cols` gate logits a token
-//                   (one per head, or one per output value).
+//                   (one per head, or one per output value).  A head may hold `maps` vectors of equal
+//                   size side by side (the queries and keys of several attention maps over one set of
+//                   values); each is turned by itself over its own first `rot` values.  `magnitude`
+//                   multiplies every cosine and sine (1: a pure rotation).
 //   attn_sink       one warp per (query token, query head) walks the visible keys 32 at a time with
 //                   an online softmax in float32: score = cap * tanh(scale * q.k / cap) (cap 0: none);
 //                   a query at position p sees keys j <= p with j >= p - window + 1 (window > 0) and
@@ -118,7 +121,7 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
                       const int* __restrict__ token_seq, const int* __restrict__ page_table, int table_cols,
                       T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                       float* __restrict__ gate_out, int H, int G, int dk, int dv, int rot, int pairing,
-                      int norm_heads, int gate_cols, int page_size, float eps) {
+                      int norm_heads, int gate_cols, int page_size, float eps, int maps, float magnitude) {
     extern __shared__ float turned[];  // [8 warps][dk]
     pdl_wait();
     pdl_launch_dependents();
@@ -130,6 +133,7 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
     const float* row = a + (size_t)n * (nq + nk + nv + gate_cols);
     const float p = (float)pos;
     const int half = rot >> 1;
+    const int sub = dk / maps;  // the size of one map's vector
     size_t cache_row = 0;
     if (G) {
         int page = page_table[(size_t)token_seq[n] * table_cols + pos / page_size];
@@ -143,20 +147,21 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
         float ss = 0.f;
         for (int i = lane; i < dk; i += 32) {
             float x = src[i];
-            if (i < rot) {
+            const int j = i % sub;  // the place within its map's vector
+            if (j < rot) {
                 int f, other;
                 bool first;
                 if (pairing) {
-                    first = i < half;
-                    f = first ? i : i - half;
+                    first = j < half;
+                    f = first ? j : j - half;
                     other = first ? i + half : i - half;
                 } else {
-                    first = (i & 1) == 0;
-                    f = i >> 1;
+                    first = (j & 1) == 0;
+                    f = j >> 1;
                     other = i ^ 1;
                 }
                 const float ang = p * freq[f];
-                const float c = cosf(ang), s = sinf(ang), y = src[other];
+                const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude, y = src[other];
                 x = first ? x * c - y * s : x * c + y * s;
             }
             buf[i] = x;
@@ -568,16 +573,20 @@ NNIS_API int nnis_qkv_prep(const float* a, const float* wq, const float* wk, con
 }
 
 // a: float32 [n, H dk + G dk + G dv + gate_cols]; q_scale: float32 [H] or null; pairing 0: neighbours,
-// 1: halves; norm_heads: every q and k head divided by its own root mean square after the rotation
+// 1: halves; norm_heads: every q and k head divided by its own root mean square after the rotation;
+// maps: vectors of dk / maps values side by side in a head, each turned by itself; magnitude: a
+// multiplier of every cosine and sine
 NNIS_API int nnis_qkv_prep_heads(const float* a, const float* q_scale, const float* freq, const int* token_pos,
                                  const int* token_seq, const int* page_table, int table_cols, void* q_out,
                                  void* k_cache, void* v_cache, float* gate_out, int n_tokens, int H, int G, int dk,
                                  int dv, int rot, int pairing, int norm_heads, int gate_cols, int page_size,
-                                 float eps, int dtype, cudaStream_t stream) {
+                                 float eps, int maps, float magnitude, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || H <= 0 || G < 0 || dk <= 0 || dv <= 0 || rot < 0 || gate_cols < 0 || !a || !q_out ||
         !token_pos)
         return NNIS_ERR_ARGUMENT;
-    if ((rot & 1) || rot > dk || dk > 1024) return NNIS_ERR_UNSUPPORTED;
+    if (maps <= 0 || dk % maps) return NNIS_ERR_ARGUMENT;
+    if ((rot & 1) || rot > dk / maps || dk > 1024 || ((dk / maps) & 1 && maps > 1 && !pairing))
+        return NNIS_ERR_UNSUPPORTED;
     if (rot > 0 && !freq) return NNIS_ERR_ARGUMENT;
     if (G > 0 && (!k_cache || !v_cache || !page_table || !token_seq || page_size <= 0)) return NNIS_ERR_ARGUMENT;
     if (gate_cols && !gate_out) return NNIS_ERR_ARGUMENT;
@@ -587,12 +596,12 @@ NNIS_API int nnis_qkv_prep_heads(const float* a, const float* q_scale, const flo
         e = launch_dependent(qkv_prep_heads_kernel<float>, (unsigned)n_tokens, 256, smem, stream, a, q_scale, freq,
                              token_pos, token_seq, page_table, table_cols, (float*)q_out, (float*)k_cache,
                              (float*)v_cache, gate_out, H, G, dk, dv, rot, pairing, norm_heads, gate_cols, page_size,
-                             eps);
+                             eps, maps, magnitude);
     else if (dtype == NNIS_DTYPE_BF16)
         e = launch_dependent(qkv_prep_heads_kernel<bf16>, (unsigned)n_tokens, 256, smem, stream, a, q_scale, freq,
                              token_pos, token_seq, page_table, table_cols, (bf16*)q_out, (bf16*)k_cache,
                              (bf16*)v_cache, gate_out, H, G, dk, dv, rot, pairing, norm_heads, gate_cols, page_size,
-                             eps);
+                             eps, maps, magnitude);
     else
         return NNIS_ERR_UNSUPPORTED;
     return e == cudaSuccess ? NNIS_OK : (int)e;

@@ -12,7 +12,7 @@
 //   softcap_rows     x <- cap * tanh(x / cap), float32 in place (logits)
 //   act_rows         a plain activation of float32 rows, rounded once to the operand dtype:
 //                    gelu with erf, 0.5 z (1 + erf(z / sqrt 2)), or its tanh form,
-//                    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))
+//                    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), or the square of relu
 //   depth_mix        keeps a block's result among the results of the blocks before it and
 //                    replaces the stream by a weighted sum of them all:
 //                    history[terms - 1] = hidden; hidden = sum_j w[j] history[j]
@@ -207,6 +207,7 @@ __global__ void act_rows_kernel(const float* __restrict__ x, T* __restrict__ out
     const float z = x[i];
     float y;
     if (kind == 0) y = 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+    else if (kind == 2) y = fmaxf(z, 0.f) * fmaxf(z, 0.f);
     else y = 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
     out[i] = from_float<T>(y);
 }
@@ -232,7 +233,7 @@ using namespace nnis;
 // kind 0: gelu (erf); 1: gelu (tanh form)
 NNIS_API int nnis_act_rows(const float* x, void* out, int out_dtype, long long count, int kind,
                            cudaStream_t stream) {
-    if (count <= 0 || !x || !out || kind < 0 || kind > 1) return NNIS_ERR_ARGUMENT;
+    if (count <= 0 || !x || !out || kind < 0 || kind > 2) return NNIS_ERR_ARGUMENT;
     unsigned blocks = (unsigned)((count + 255) / 256);
     cudaError_t e;
     if (out_dtype == NNIS_DTYPE_F32)

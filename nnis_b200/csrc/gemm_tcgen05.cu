@@ -718,10 +718,10 @@ NNIS_API int nnis_gemm_tc_glu_clamp(const void* A, const void* W, const float* b
 }
 
 // The storing product (mode 0) with an activation in its epilogue: out [M, N] = bf16(act(A . W^T + bias)),
-// `act` 2: gelu with erf; 3: gelu's tanh form.
+// `act` 1: the square of relu; 2: gelu with erf; 3: gelu's tanh form.
 NNIS_API int nnis_gemm_tc_act(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int act,
                               int sm_count, int* status, int pdl, cudaStream_t stream) {
-    if (act != nnis::GEMM_ACT_GELU_ERF && act != nnis::GEMM_ACT_GELU_TANH) return NNIS_ERR_ARGUMENT;
+    if (act < nnis::GEMM_ACT_RELU2 || act > nnis::GEMM_ACT_GELU_TANH) return NNIS_ERR_ARGUMENT;
     return gemm_tc_run(A, W, bias, C, M, N, K, 0, nullptr, nullptr, nullptr, 0, nullptr, nullptr, nullptr, nullptr,
                        0, 0, 0, 0, nullptr, 0, nullptr, 0, sm_count, status, pdl, stream, 0.f, 0.f, act);
 }

@@ -180,7 +180,7 @@ NNIS_API int nnis_gemv_grid(int M, int N, int K, int sm_count) {
 // `emit_w` [N] in bfloat16 [M, N], and per row and eight columns the sum of the output's
 // squares [M, N / 8], for a product that follows with `ss_parts` [M, K / 8]: x is then such
 // an `emit_x`, and `eps` the norm's (the kernel over tiles of rows only).
-// `act` (STORE, optional): 2 stores gelu (erf) of the sums, 3 gelu's tanh form.
+// `act` (STORE, optional): 1 stores the square of relu of the sums, 2 gelu (erf), 3 gelu's tanh form.
 NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows, const float* norm_w,
                             float eps, const void* w, const float* bias, void* out, int M, int N,
                             int K, int epilogue, const int* token_pos, const int* token_seq,
@@ -192,7 +192,7 @@ NNIS_API int nnis_gemv_bf16(const void* x, const float* hidden, const int* rows,
                             int sm_count, int pdl, cudaStream_t stream) {
     using namespace nnis;
     if (M <= 0 || N <= 0 || K <= 0 || !w || !out) return NNIS_ERR_ARGUMENT;
-    if (act && (epilogue != EPI_STORE || (act != 2 && act != 3))) return NNIS_ERR_ARGUMENT;
+    if (act && (epilogue != EPI_STORE || act < 1 || act > 3)) return NNIS_ERR_ARGUMENT;
     GemvPlan plan;
     plan.kc = K;
     int pro = hidden ? PRO_NORM : ss_parts ? PRO_SCALED : PRO_PLAIN;

@@ -87,12 +87,16 @@ struct GemvArgs {
     // PRO_SCALED prologue: those shares of the rows' sums of squares, [M, ss_units]
     const float* ss_parts;
     int ss_units;
-    // STORE epilogue, optional: an activation on the sums before they are rounded; 0 none, 2 gelu with
-    // erf, 3 gelu's tanh form (the codes of the tensor-core product's storing epilogue)
+    // STORE epilogue, optional: an activation on the sums before they are rounded; 0 none, 1 the square of
+    // relu, 2 gelu with erf, 3 gelu's tanh form (the codes of the tensor-core product's storing epilogue)
     int act;
 };
 
 __device__ __forceinline__ float gemv_act(float z, int act) {
+    if (act == 1) {
+        z = fmaxf(z, 0.f);
+        return z * z;
+    }
     if (act == 2) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
     if (act == 3) return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
     return z;

@@ -17,6 +17,19 @@
 //                  the score multiplies both float32 sums, which is the product with w * h
 //   moe_down       with no weights: the chosen experts' outputs are added as they are
 //
+// A third form serves routers that score ALL their outputs with one softmax and choose by those
+// scores plus a correction per output, group by group, and whose last outputs stand for experts
+// that hand their input on unchanged:
+//
+//   moe_route_choice  s = softmax(z) over all `outputs`; choice c = s + correction; the outputs form
+//                     `groups` equal runs of neighbours, a run's score is its largest c, and only the
+//                     `keep` best runs can be chosen (the others' c counts as minus infinity); the `top`
+//                     largest c (ties to the lower index) are chosen and weighed by their s as it is.
+//                     Outputs from `experts` on have no matrices: their id is written as -1 and their
+//                     weights are added up in `pass_weight[n]`
+//   moe_up_gated      with no weights: act = silu(g) * u; a pair whose id is negative is skipped
+//   moe_down          with weights on the outputs, skipping negative ids, plus pass_weight[n] * h[n]
+//
 // Expert weights are stacked: W_up [experts, ff, width] (gated: [experts, 2 ff, width], row 2f the
 // gate's and row 2f + 1 the up-projection's of feature f), W_down [experts, width, ff].
 // A row whose position is -1 (padding) is skipped everywhere.
@@ -129,6 +142,123 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
     for (int s = lane; s < top; s += 32) wt[s] *= inv;
 }
 
+// z: [outputs] scores, then [outputs] choices, then [groups] the runs' best
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_route_choice_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
+                        const int* __restrict__ token_pos, int* __restrict__ ids, float* __restrict__ weights,
+                        float* __restrict__ pass_weight, int width, int outputs, int experts, int top, int groups,
+                        int keep) {
+    extern __shared__ float z[];
+    float* choice = z + outputs;
+    float* run_best = choice + outputs;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n = blockIdx.x;
+    int* id = ids + (size_t)n * top;
+    float* wt = weights + (size_t)n * top;
+    if (token_pos[n] < 0) {
+        for (int s = threadIdx.x; s < top; s += 256) {
+            id[s] = -1;
+            wt[s] = 0.f;
+        }
+        if (threadIdx.x == 0) pass_weight[n] = 0.f;
+        return;
+    }
+    const T* x = h + (size_t)n * width;
+    const bool by_four = (width & 3) == 0;
+    for (int e = warp; e < outputs; e += 8) {
+        const float* w = wr + (size_t)e * width;
+        float acc = 0.f;
+        if (by_four) {
+#pragma unroll 4
+            for (int i = lane * 4; i < width; i += 128) {
+                float4 wv = load4(w + i), xv = load4(x + i);
+                acc = fmaf(wv.x, xv.x, acc);
+                acc = fmaf(wv.y, xv.y, acc);
+                acc = fmaf(wv.z, xv.z, acc);
+                acc = fmaf(wv.w, xv.w, acc);
+            }
+        } else {
+            for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // one softmax over all outputs
+    float mx = -FLT_MAX;
+    for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < outputs; e += 32) {
+        const float p = expf(z[e] - mx);
+        z[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < outputs; e += 32) {
+        const float s = z[e] * inv;
+        z[e] = s;
+        choice[e] = s + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        const int size = outputs / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, choice[e]);
+            run_best[g] = best;
+        }
+        __syncwarp();
+        // the runs that are NOT among the `keep` best: a run is kept if fewer than `keep` runs beat it
+        // (a run beats another with a larger score, or an equal score and a lower index)
+        for (int g = lane; g < groups; g += 32) {
+            const float mine = run_best[g];
+            int ahead = 0;
+            for (int o = 0; o < groups; ++o) ahead += (run_best[o] > mine || (run_best[o] == mine && o < g)) ? 1 : 0;
+            if (ahead >= keep)
+                for (int e = g * size; e < (g + 1) * size; ++e) choice[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float passed = 0.f;
+    for (int s = 0; s < top; ++s) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < outputs; e += 32) {
+            const float v = choice[e];
+            if (v > best || (v == best && arg == 0x7fffffff && !isnan(v))) {  // (ascending e: the lower index wins a tie)
+                best = v;
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        const float score = z[arg];
+        if (arg >= experts) passed += score;
+        __syncwarp();
+        if (lane == 0) {
+            id[s] = arg < experts ? arg : -1;
+            wt[s] = score;
+            choice[arg] = -INFINITY;  // (chosen once)
+            z[arg] = 0.f;             // (a second pick of an exhausted list would weigh nothing)
+        }
+        __syncwarp();
+    }
+    if (lane == 0) pass_weight[n] = passed;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ h, const T* __restrict__ w_up, const int* __restrict__ ids,
@@ -160,7 +290,7 @@ moe_up_gated_kernel(const T* __restrict__ h, const T* __restrict__ w_gu, const i
     long long pair = blockIdx.x;
     int f = blockIdx.y * 8 + warp;
     long long n = pair / top;
-    if (f >= ff || token_pos[n] < 0) return;
+    if (f >= ff || token_pos[n] < 0 || ids[pair] < 0) return;
     const T* wg = w_gu + ((size_t)ids[pair] * 2 * ff + 2 * f) * width;  // (rows interleaved: gate, up)
     const T* wu = wg + width;
     const T* x = h + (size_t)n * width;
@@ -178,15 +308,18 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, const int* __restrict__ ids,
                 const float* __restrict__ weights, const int* __restrict__ token_pos,
-                float* __restrict__ residual, int width, int ff, int top) {
+                float* __restrict__ residual, int width, int ff, int top,
+                const float* __restrict__ pass_weight, const T* __restrict__ h) {
     pdl_wait();
     pdl_launch_dependents();
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     long long n = blockIdx.x;
     int c = blockIdx.y * 8 + warp;
     if (c >= width || token_pos[n] < 0) return;
-    float sum = 0.f;
+    // (what the experts that hand their input on add: their weights' sum times the input)
+    float sum = pass_weight ? pass_weight[n] * to_float(h[(size_t)n * width + c]) : 0.f;
     for (int s = 0; s < top; ++s) {
+        if (ids[n * top + s] < 0) continue;
         const T* w = w_down + ((size_t)ids[n * top + s] * width + c) * ff;
         const T* a = act + ((size_t)n * top + s) * ff;
         float acc = warp_row_dot(w, a, ff, lane);
@@ -237,13 +370,13 @@ NNIS_API int nnis_moe_experts(const void* h, const void* w_up, const void* w_dow
                              token_pos, (float*)act, width, ff, top);
         if (e == cudaSuccess)
             e = launch_dependent(moe_down_kernel<float>, down_grid, 256, 0, stream, (const float*)act,
-                                 (const float*)w_down, ids, weights, token_pos, residual, width, ff, top);
+                                 (const float*)w_down, ids, weights, token_pos, residual, width, ff, top, (const float*)nullptr, (const float*)nullptr);
     } else if (dtype == NNIS_DTYPE_BF16) {
         e = launch_dependent(moe_up_kernel<bf16>, up_grid, 256, 0, stream, (const bf16*)h, (const bf16*)w_up, ids,
                              token_pos, (bf16*)act, width, ff, top);
         if (e == cudaSuccess)
             e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
-                                 (const bf16*)w_down, ids, weights, token_pos, residual, width, ff, top);
+                                 (const bf16*)w_down, ids, weights, token_pos, residual, width, ff, top, (const float*)nullptr, (const bf16*)nullptr);
     } else {
         return NNIS_ERR_UNSUPPORTED;
     }
@@ -268,14 +401,75 @@ NNIS_API int nnis_moe_experts_gated(const void* h, const void* w_gu, const void*
         if (e == cudaSuccess)
             e = launch_dependent(moe_down_kernel<float>, down_grid, 256, 0, stream, (const float*)act,
                                  (const float*)w_down, ids, (const float*)nullptr, token_pos, residual, width, ff,
-                                 top);
+                                 top, (const float*)nullptr, (const float*)nullptr);
     } else if (dtype == NNIS_DTYPE_BF16) {
         e = launch_dependent(moe_up_gated_kernel<bf16>, up_grid, 256, 0, stream, (const bf16*)h, (const bf16*)w_gu,
                              ids, weights, token_pos, (bf16*)act, width, ff, top);
         if (e == cudaSuccess)
             e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
                                  (const bf16*)w_down, ids, (const float*)nullptr, token_pos, residual, width, ff,
-                                 top);
+                                 top, (const float*)nullptr, (const bf16*)nullptr);
+    } else {
+        return NNIS_ERR_UNSUPPORTED;
+    }
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+// The router that scores all its outputs with one softmax: see moe_route_choice above.  wr float32
+// [outputs, width]; correction float32 [outputs] or null; ids int32 [n, top] (-1: an output from
+// `experts` on); weights float32 [n, top]; pass_weight float32 [n].
+NNIS_API int nnis_moe_route_choice(const void* h, const float* wr, const float* correction, const int* token_pos,
+                                   int* ids, float* weights, float* pass_weight, int n_tokens, int width,
+                                   int outputs, int experts, int top, int groups, int keep, int dtype,
+                                   cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0 || outputs <= 0 || experts < 0 || experts > outputs || top <= 0 ||
+        top > outputs || groups <= 0 || outputs % groups || keep <= 0 || keep > groups || !h || !wr || !ids ||
+        !weights || !pass_weight || !token_pos)
+        return NNIS_ERR_ARGUMENT;
+    if (top > keep * (outputs / groups)) return NNIS_ERR_ARGUMENT;
+    size_t smem = (2 * (size_t)outputs + groups) * sizeof(float);
+    if (smem > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
+    unsigned blocks = (unsigned)n_tokens;
+    cudaError_t e;
+    if (dtype == NNIS_DTYPE_F32)
+        e = launch_dependent(moe_route_choice_kernel<float>, blocks, 256, smem, stream, (const float*)h, wr,
+                             correction, token_pos, ids, weights, pass_weight, width, outputs, experts, top, groups,
+                             keep);
+    else if (dtype == NNIS_DTYPE_BF16)
+        e = launch_dependent(moe_route_choice_kernel<bf16>, blocks, 256, smem, stream, (const bf16*)h, wr, correction,
+                             token_pos, ids, weights, pass_weight, width, outputs, experts, top, groups, keep);
+    else
+        return NNIS_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? NNIS_OK : (int)e;
+}
+
+// Gated experts whose weights multiply their OUTPUTS; a pair with a negative id has no expert;
+// pass_weight (float32 [n] or null) times the token's input is added too.
+NNIS_API int nnis_moe_experts_gated_out(const void* h, const void* w_gu, const void* w_down, const int* ids,
+                                        const float* weights, const float* pass_weight, const int* token_pos,
+                                        void* act, float* residual, int n_tokens, int width, int ff, int top,
+                                        int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || width <= 0 || ff <= 0 || top <= 0 || !h || !w_gu || !w_down || !ids || !weights ||
+        !token_pos || !act || !residual)
+        return NNIS_ERR_ARGUMENT;
+    if ((ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535) return NNIS_ERR_UNSUPPORTED;
+    dim3 up_grid((unsigned)((long long)n_tokens * top), (ff + 7) / 8);
+    dim3 down_grid(n_tokens, (width + 7) / 8);
+    cudaError_t e;
+    if (dtype == NNIS_DTYPE_F32) {
+        e = launch_dependent(moe_up_gated_kernel<float>, up_grid, 256, 0, stream, (const float*)h, (const float*)w_gu,
+                             ids, (const float*)nullptr, token_pos, (float*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<float>, down_grid, 256, 0, stream, (const float*)act,
+                                 (const float*)w_down, ids, weights, token_pos, residual, width, ff, top, pass_weight,
+                                 (const float*)h);
+    } else if (dtype == NNIS_DTYPE_BF16) {
+        e = launch_dependent(moe_up_gated_kernel<bf16>, up_grid, 256, 0, stream, (const bf16*)h, (const bf16*)w_gu,
+                             ids, (const float*)nullptr, token_pos, (bf16*)act, width, ff, top);
+        if (e == cudaSuccess)
+            e = launch_dependent(moe_down_kernel<bf16>, down_grid, 256, 0, stream, (const bf16*)act,
+                                 (const bf16*)w_down, ids, weights, token_pos, residual, width, ff, top, pass_weight,
+                                 (const bf16*)h);
     } else {
         return NNIS_ERR_UNSUPPORTED;
     }

@@ -232,7 +232,7 @@ def sample_temperature(logits: torch.Tensor, temperature: torch.Tensor, rng_stat
 
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_GATED, EPI_QKV, EPI_ARGMAX = 0, 1, 2, 3, 4, 5
 # activations that the storing epilogues of the bfloat16 products can apply (gelu with erf, its tanh form)
-GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH = 2, 3
+GEMM_ACT_RELU2, GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH = 1, 2, 3
 # programmatic dependent launch between the decode kernels (NNIS_PDL=0 turns it off)
 PDL = 0 if os.environ.get("NNIS_PDL", "1") == "0" else 1
 # The QKV projection of a decode step lets attention_decode_tma start with it instead of after
@@ -399,7 +399,7 @@ def gemv_bf16(w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, 
               "gemv: emit shares float32 [m, n / 8]")
     if bias is not None:
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemv: bias float32 [n]")
-    _need(act == 0 or (epilogue == EPI_STORE and act in (GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH)),
+    _need(act == 0 or (epilogue == EPI_STORE and act in (GEMM_ACT_RELU2, GEMM_ACT_GELU_ERF, GEMM_ACT_GELU_TANH)),
           "gemv: an activation goes with the storing epilogue")
     if epilogue == EPI_STORE:
         _need(out.dtype == torch.bfloat16 and tuple(out.shape) == (m, n), "gemv: out bfloat16 [m, n]")
@@ -895,7 +895,7 @@ def gemm_tc_glu_clamp(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Ten
 
 def gemm_tc_act(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, act: int) -> None:
     """The storing tensor-core product with an activation in its epilogue: out bfloat16 [m, n] =
-    act(a . w^T + bias); ``GEMM_ACT_GELU_ERF`` or ``GEMM_ACT_GELU_TANH``."""
+    act(a . w^T + bias); ``GEMM_ACT_RELU2``, ``GEMM_ACT_GELU_ERF`` or ``GEMM_ACT_GELU_TANH``."""
     _cuda(a, w, bias, out)
     m, k = a.shape
     n = w.shape[0]
@@ -1544,14 +1544,16 @@ def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Ten
              page_table: Optional[torch.Tensor], q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
              v_cache: Optional[torch.Tensor], gate_out: Optional[torch.Tensor], heads: int, kv_heads: int,
              dk: int, dv: int, rot: int, eps: float, pairing: str = "neighbours", head_norm: bool = False,
-             q_scale: Optional[torch.Tensor] = None) -> None:
+             q_scale: Optional[torch.Tensor] = None, maps: int = 1, magnitude: float = 1.0) -> None:
     """From float32 rows [q | k | v | gate logits]: norms of q and k, rotation, q packed, k and v into
     the cache, sigmoid of the gate's logits (``gate_out`` [n, heads] or [n, heads * dv]: as many logits a
     row).  ``kv_heads == 0``: the rows hold no keys and values.  Two forms: with ``wq``/``wk`` the
     norms go over the whole projections, before the rotation of neighbouring pairs; with
     ``head_norm``, ``pairing == "half"``, ``q_scale`` (float32 [heads], a multiplier of each head's
     q) or a gate per value, everything is per head: the rotation (either pairing), then optionally
-    every head divided by its own root mean square."""
+    every head divided by its own root mean square.  ``maps`` > 1: a head of q or k holds that many
+    vectors of dk / maps values side by side, each turned by itself over its first ``rot`` values;
+    ``magnitude`` multiplies every cosine and sine."""
     _cuda(a, wq, wk, freq, token_pos, token_seq, page_table, q_out, k_cache, v_cache, gate_out, q_scale)
     n = a.shape[0]
     gate_cols = 0 if gate_out is None else gate_out.shape[1]
@@ -1571,7 +1573,9 @@ def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Ten
               "qkv_prep: caches [pages, kv_heads, page, dk] and [.., dv]")
         _need(page_table is not None and page_table.dtype == torch.int32, "qkv_prep: page_table int32")
         cols, page_size = page_table.shape[1], k_cache.shape[2]
-    per_head = head_norm or pairing == "half" or q_scale is not None or gate_cols not in (0, heads)
+    per_head = head_norm or pairing == "half" or q_scale is not None or gate_cols not in (0, heads) \
+        or maps != 1 or magnitude != 1.0
+    _need(maps >= 1 and dk % maps == 0 and rot <= dk // maps, "qkv_prep: maps vectors of equal size in a head")
     if per_head:
         _need(wq is None and wk is None, "qkv_prep: the per-head form has no norm over the whole projections")
         _need(q_scale is None or (q_scale.dtype == torch.float32 and q_scale.numel() == heads),
@@ -1580,7 +1584,8 @@ def qkv_prep(a: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Ten
                                           _ptr(page_table), cols, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
                                           _ptr(gate_out), n, heads, kv_heads, dk, dv, rot,
                                           1 if pairing == "half" else 0, 1 if head_norm else 0, gate_cols,
-                                          page_size, ctypes.c_float(eps), code_of(q_out.dtype), _stream()),
+                                          page_size, ctypes.c_float(eps), maps, ctypes.c_float(magnitude),
+                                          code_of(q_out.dtype), _stream()),
                "qkv_prep_heads")
         return
     _check(_lib().nnis_qkv_prep(_ptr(a), _ptr(wq), _ptr(wk), _ptr(freq), _ptr(token_pos), _ptr(token_seq),
@@ -1719,11 +1724,11 @@ def moe_grouped_gated_tc(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tens
            "moe_grouped_gated_tc", 6)
 
 
-GELU_ERF, GELU_TANH = 0, 1
+GELU_ERF, GELU_TANH, RELU2 = 0, 1, 2
 
 
 def act_rows(x: torch.Tensor, out: torch.Tensor, kind: int) -> None:
-    """out = activation(x), x float32, rounded once to out's dtype; ``GELU_ERF`` or ``GELU_TANH``."""
+    """out = activation(x), x float32, rounded once to out's dtype; ``GELU_ERF``, ``GELU_TANH`` or ``RELU2``."""
     _cuda(x, out)
     _need(x.dtype == torch.float32 and x.numel() == out.numel(), "act_rows: float32 in, as many values out")
     _check(_lib().nnis_act_rows(_ptr(x), _ptr(out), code_of(out.dtype), ctypes.c_longlong(x.numel()), kind,
@@ -1824,3 +1829,141 @@ def delta_finish(o_raw: torch.Tensor, gate_rows: torch.Tensor, gate_off: int, we
     _check(_lib().nnis_delta_finish(_ptr(o_raw), _ptr(gate_rows), gate_rows.shape[1], gate_off, _ptr(weight),
                                     _ptr(token_pos), _ptr(out), n, heads, vdim, ctypes.c_float(eps),
                                     code_of(out.dtype), _stream()), "delta_finish")
+
+
+# ---------------------------------------------------------------------------
+# steps on the stream outside the sub-layers (stream_steps.cu)
+# ---------------------------------------------------------------------------
+def embed_pair(table: torch.Tensor, pair: Optional[torch.Tensor], tokens: torch.Tensor, token_pos: torch.Tensor,
+               token_seq: torch.Tensor, seq_slots: torch.Tensor, seq_count: Optional[torch.Tensor],
+               last_token: Optional[torch.Tensor], hidden: torch.Tensor, status: torch.Tensor, scale: float,
+               buckets: int, mul_prev: int, mul_cur: int) -> None:
+    """hidden[n] = table[token] * scale + pair[(token before * mul_prev + token * mul_cur) mod buckets],
+    row ``buckets`` of ``pair`` for a sequence's first token.  The token before a step's first row of a
+    sequence is ``last_token[slot]``, which then takes the step's last token of that sequence
+    (``seq_count``: tokens per sequence of the step; None: one each).  ``pair`` None: no second table."""
+    _cuda(table, pair, tokens, token_pos, token_seq, seq_slots, seq_count, last_token, hidden, status)
+    n, width = hidden.shape
+    _need(tokens.dtype == torch.int32 and tokens.numel() >= n and token_pos.numel() >= n, "embed_pair: int32 [n]")
+    _need(hidden.dtype == torch.float32 and table.shape[1] == width, "embed_pair: hidden float32 [n, width]")
+    if pair is not None:
+        _need(pair.dtype == table.dtype and tuple(pair.shape) == (buckets + 1, width),
+              "embed_pair: pair table [buckets + 1, width] of the table's dtype")
+        _need(last_token is not None and last_token.dtype == torch.int32, "embed_pair: last_token int32 [slots]")
+    _check(_lib().nnis_embed_pair(_ptr(table), _ptr(pair), code_of(table.dtype), _ptr(tokens), _ptr(token_pos),
+                                  _ptr(token_seq), _ptr(seq_slots), _ptr(seq_count), _ptr(last_token), _ptr(hidden),
+                                  n, width, table.shape[0], buckets, ctypes.c_longlong(mul_prev),
+                                  ctypes.c_longlong(mul_cur), ctypes.c_float(scale), _ptr(status), _stream()),
+           "embed_pair")
+
+
+def rmsnorm_pair(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, eps: float, out1: torch.Tensor,
+                 out2: torch.Tensor) -> None:
+    """Two RMS norms of the same float32 rows in one pass: out1 = x / rms * w1, out2 = x / rms * w2."""
+    _cuda(x, w1, w2, out1, out2)
+    n, width = out1.shape
+    _need(x.dtype == torch.float32 and tuple(x.shape) == (n, width) and tuple(out2.shape) == (n, width)
+          and out1.dtype == out2.dtype, "rmsnorm_pair: x float32 [n, width], two outputs alike")
+    _need(w1.dtype == w2.dtype == torch.float32 and w1.numel() == w2.numel() == width,
+          "rmsnorm_pair: weights float32 [width]")
+    _check(_lib().nnis_rmsnorm_pair(_ptr(x), _ptr(w1), _ptr(w2), _ptr(out1), _ptr(out2), code_of(out1.dtype), n,
+                                    width, ctypes.c_float(eps), _stream()), "rmsnorm_pair")
+
+
+def stream_enter(hidden: torch.Tensor, kept: Optional[torch.Tensor], row: Optional[torch.Tensor]) -> None:
+    """hidden += kept (float32, the same shape) + row (float32 [width]); either may be None."""
+    _cuda(hidden, kept, row)
+    _need(hidden.dtype == torch.float32 and hidden.dim() == 2, "stream_enter: hidden float32 [n, width]")
+    _need(kept is None or (kept.dtype == torch.float32 and kept.shape == hidden.shape), "stream_enter: kept")
+    _need(row is None or (row.dtype == torch.float32 and row.numel() == hidden.shape[1]), "stream_enter: row")
+    _check(_lib().nnis_stream_enter(_ptr(hidden), _ptr(kept), _ptr(row), ctypes.c_longlong(hidden.numel()),
+                                    hidden.shape[1], _stream()), "stream_enter")
+
+
+def scale_rows(x: torch.Tensor, s: float) -> None:
+    """x *= s on float32 values."""
+    _cuda(x)
+    _need(x.dtype == torch.float32, "scale_rows: float32")
+    if x.numel():
+        _check(_lib().nnis_scale_rows(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(s), _stream()),
+               "scale_rows")
+
+
+# ---------------------------------------------------------------------------
+# differential attention (attention_diff.cu)
+# ---------------------------------------------------------------------------
+def attention_diff(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
+                   token_seq: torch.Tensor, page_table: torch.Tensor, gate: Optional[torch.Tensor],
+                   out: torch.Tensor, heads: int, kv_heads: int, window: int, scale: float, lam: float,
+                   post: float, eps: float, n_splits: int = 1, partial: Optional[torch.Tensor] = None) -> None:
+    """Two attention maps a head over the same values: q [n, heads * 2 dk], key rows [k1 | k2] of 2 dk,
+    out = rms(a1 - lam * a2) * post * gate over each head's dv values (gate float32 [n, heads * dv])."""
+    _cuda(q, k_cache, v_cache, token_pos, token_seq, page_table, gate, out, partial)
+    n = out.shape[0]
+    pages, nkv, page_size, dk2 = k_cache.shape
+    dv = v_cache.shape[3]
+    _need(dk2 % 2 == 0 and nkv == kv_heads and tuple(v_cache.shape[:3]) == (pages, nkv, page_size)
+          and heads % kv_heads == 0, "attention_diff: caches [pages, kv_heads, page, 2 dk / dv]")
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype and tuple(q.shape) == (n, heads * dk2)
+          and tuple(out.shape) == (n, heads * dv), "attention_diff: q [n, heads * 2 dk], out [n, heads * dv]")
+    _need(pages * nkv * page_size < 2 ** 31, "attention_diff: the cache has too many rows")
+    _need(gate is None or (gate.dtype == torch.float32 and tuple(gate.shape) == (n, heads * dv)),
+          "attention_diff: gate float32 [n, heads * dv]")
+    if n_splits > 1:
+        _need(partial is not None and partial.dtype == torch.float32
+              and partial.numel() >= n * heads * n_splits * (2 * dv + 4), "attention_diff: partial scratch")
+    _check(_lib().nnis_attention_diff(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+                                      _ptr(page_table), page_table.shape[1], _ptr(gate), _ptr(out), _ptr(partial),
+                                      n, heads, kv_heads, dk2 // 2, dv, page_size, window, ctypes.c_float(scale),
+                                      ctypes.c_float(lam), ctypes.c_float(post), ctypes.c_float(eps), n_splits,
+                                      code_of(out.dtype), _stream()), "attention_diff", 2 if n_splits > 1 else 1)
+
+
+# ---------------------------------------------------------------------------
+# experts chosen by corrected scores, group by group (moe.cu)
+# ---------------------------------------------------------------------------
+def moe_route_choice(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+                     token_pos: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, pass_weight: torch.Tensor,
+                     experts: int, top: int, groups: int = 1, keep: int = 1) -> None:
+    """Scores s = softmax over ALL outputs of the router; chosen: the ``top`` largest s + correction among
+    the ``keep`` best of ``groups`` equal runs of neighbours; weights = the chosen s, as they are.  Outputs
+    from ``experts`` on have no expert: ids -1, their weights summed in ``pass_weight`` [n]."""
+    _cuda(h, w_router, correction, token_pos, ids, weights, pass_weight)
+    n, width = h.shape
+    outputs = w_router.shape[0]
+    _need(w_router.dtype == torch.float32 and w_router.shape[1] == width, "moe_route_choice: router float32")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.numel() == outputs),
+          "moe_route_choice: correction float32 [outputs]")
+    _need(ids.dtype == torch.int32 and weights.dtype == pass_weight.dtype == torch.float32
+          and ids.numel() >= n * top and weights.numel() >= n * top and pass_weight.numel() >= n,
+          "moe_route_choice: ids int32 [n, top], weights float32 [n, top], pass_weight float32 [n]")
+    _check(_lib().nnis_moe_route_choice(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(token_pos), _ptr(ids),
+                                        _ptr(weights), _ptr(pass_weight), n, width, outputs, experts, top, groups,
+                                        keep, code_of(h.dtype), _stream()), "moe_route_choice")
+
+
+def moe_experts_gated_out(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
+                          weights: torch.Tensor, pass_weight: Optional[torch.Tensor], token_pos: torch.Tensor,
+                          act: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+    """residual[n] += sum over the chosen experts of weight * W_down[e] (silu(W_gate[e] h) * (W_up[e] h))
+    + pass_weight[n] * h[n]; a negative id has no expert."""
+    _cuda(h, w_gu, w_down, ids, weights, pass_weight, token_pos, act, residual)
+    n, width = h.shape
+    experts, ff2, _ = w_gu.shape
+    ff = ff2 // 2
+    _need(tuple(w_gu.shape) == (experts, 2 * ff, width) and tuple(w_down.shape) == (experts, width, ff)
+          and h.dtype == w_gu.dtype == w_down.dtype == act.dtype, "moe_experts_gated_out: stacked weights of one dtype")
+    _need(act.numel() >= n * top * ff, "moe_experts_gated_out: act scratch [n, top, ff]")
+    _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_experts_gated_out: residual")
+    _check(_lib().nnis_moe_experts_gated_out(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights),
+                                             _ptr(pass_weight), _ptr(token_pos), _ptr(act), _ptr(residual), n, width,
+                                             ff, top, code_of(h.dtype), _stream()), "moe_experts_gated_out", 2)
+
+
+DIFF_MMA = 0 if os.environ.get("NNIS_DIFF_MMA", "1") == "0" else 1
+
+
+def attention_diff_mma_takes(dk: int, dv: int, page_size: int) -> bool:
+    """Whether the tensor-core prompt form of differential attention takes maps of ``dk`` values and
+    values of ``dv``."""
+    return False

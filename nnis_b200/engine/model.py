@@ -28,6 +28,13 @@ class DecoderModel:
                                       self.device)
         self.head = HEADS.build(spec.head.kind, spec.head.params, "", dtype, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # what schedule entries add to the stream before their layers: tensors by name, and whether
+        # any of them wants the embedding output kept
+        self._enter_names = sorted({(e.enter.tensor, e.enter.rows) for e in spec.schedule
+                                    if e.enter is not None and e.enter.tensor is not None})
+        self._enter_tensors: Dict[str, torch.Tensor] = {}
+        self._keeps_embedding = any(e.enter is not None and e.enter.embedding for e in spec.schedule)
+        self._embedding_view = None
         for i, entry in enumerate(spec.schedule):
             wants = self.blocks[entry.layer].cache_request()
             if entry.cache_of is not None and wants is not None:
@@ -42,6 +49,8 @@ class DecoderModel:
                 if name in specs and specs[name].shape != ws.shape:
                     raise ValueError(f"tensor {name} is wanted with two shapes")
                 specs.setdefault(name, ws)
+        for name, rows in self._enter_names:
+            specs.setdefault(name, WeightSpec((rows, self.spec.hidden_size), "vector"))
         return specs
 
     @staticmethod
@@ -52,6 +61,7 @@ class DecoderModel:
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for part in (self.embedding, *self.blocks, self.final_norm, self.head):
             part.load(tensors)
+        self._enter_tensors = {name: tensors[name].to(torch.float32).contiguous() for name, _ in self._enter_names}
 
     def parameter_bytes(self) -> int:
         """Bytes of weights one step reads: each scheduled block once per run,
@@ -71,8 +81,11 @@ class DecoderModel:
 
     # -- cache ----------------------------------------------------------------
     def cache_requests(self) -> List[Optional[object]]:
+        """One request per schedule entry and, after them, the embedding's (a state of its own
+        per sequence, or None)."""
+        ask = getattr(self.embedding, "cache_request", None)
         return [None if e.cache_of is not None else self.blocks[e.layer].cache_request()
-                for e in self.spec.schedule]
+                for e in self.spec.schedule] + [ask() if ask is not None else None]
 
     def bind_cache(self, cache) -> None:
         self._views = []
@@ -81,6 +94,7 @@ class DecoderModel:
             if entry.cache_of is not None:
                 self.blocks[entry.layer].check_shared_cache(view)
             self._views.append(view)
+        self._embedding_view = cache.view(len(self.spec.schedule))
 
     def step_tables(self, counts, starts) -> Dict[str, object]:
         """The work lists that the scheduled blocks want uploaded for a prompt step."""
@@ -116,15 +130,27 @@ class DecoderModel:
 
     def _run_blocks(self, ctx) -> torch.Tensor:
         hidden = ctx.workspace.get("hidden", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
-        self.embedding.forward(ctx.tokens, hidden, self.status)
+        if getattr(self.embedding, "forward_step", None) is not None:  # (an embedding that reads the step and its state)
+            self.embedding.forward_step(ctx, hidden, self.status, self._embedding_view)
+        else:
+            self.embedding.forward(ctx.tokens, hidden, self.status)
+        kept = None
+        if self._keeps_embedding:
+            kept = ctx.workspace.get("embedding_output", (ctx.n_tokens, self.spec.hidden_size), torch.float32)
+            ops.copy_async(kept, hidden)
         ctx.hidden_copy = ctx.normed_rows = None  # (a context may run more than one step: nothing of the last one counts)
         schedule = self.spec.schedule
         for i, entry in enumerate(schedule):
-            # a block may begin the first norm of the block after it, if that one takes it
-            ask = getattr(self.blocks[schedule[i + 1].layer], "first_shared_norm", None) \
-                if i + 1 < len(schedule) else None
+            if entry.enter is not None and (entry.enter.embedding or entry.enter.tensor is not None):
+                ops.stream_enter(hidden, kept if entry.enter.embedding else None,
+                                 self._enter_tensors[entry.enter.tensor][entry.enter.row]
+                                 if entry.enter.tensor is not None else None)
+            # a block may begin the first norm of the block after it, if that one takes it (not across
+            # something that the stream takes up in between)
+            follows = i + 1 < len(schedule) and schedule[i + 1].enter is None
+            ask = getattr(self.blocks[schedule[i + 1].layer], "first_shared_norm", None) if follows else None
             ctx.next_norm = ask(ctx, ctx.n_tokens) if ask is not None else None
-            ctx.next_block = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            ctx.next_block = self.blocks[schedule[i + 1].layer] if follows else None
             self.blocks[entry.layer].forward(hidden, ctx, self._views[i])
         ctx.next_norm = ctx.next_block = ctx.shared_norm = ctx.hidden_copy = ctx.normed_rows = None
         return hidden

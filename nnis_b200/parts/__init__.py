@@ -1,4 +1,4 @@
-from . import (attention, block, delta_rule, embedding, latent_attention, mixer_pair, mlp, moe,  # noqa: F401
+from . import (attention, block, delta_rule, diff_attention, embedding, latent_attention, mixer_pair, mlp, moe,  # noqa: F401
                norm, position, retention, selective_scan, sink_attention, wkv)  # (registration)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Part,
                    PositionEncoding, Registry)

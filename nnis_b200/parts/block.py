@@ -6,7 +6,8 @@ its parts from ``LayerSpec.parts`` by the roles it knows, so one with other or m
 sub-layers (a post-norm, one norm for parallel branches, a third sub-layer) is a
 class registered in ``BLOCKS``, not a change here.
 
-``parallel``: with n = norm(h), h += mixer(n) + ffn(n); roles norm, mixer, ffn.
+``parallel``: with n = norm(h), h += mixer(n) + ffn(n); roles norm, mixer, ffn; with the role
+ffn_norm the feed-forward reads a norm of its own of the same h: h += mixer(norm(h)) + ffn(ffn_norm(h)).
 
 ``branch_norm``: h += m * norm1(mixer(h)); h += m * norm2(ffn(h)): the sub-layers read the
 stream itself and the norm stands on their OUTPUT; roles mixer, mixer_norm, and optionally
@@ -142,7 +143,9 @@ class ParallelBlock(Block):
     """One norm, two branches that both read it: with h = norm(x),
     x += mixer(h) + ffn(h).  Roles: norm, mixer and, optionally, ffn (a layer
     without a feed-forward has none).  Both branches add into the float32 residual;
-    the feed-forward reads the normed rows, which the mixer leaves as they are.
+    the feed-forward reads the normed rows, which the mixer leaves as they are.  With the optional
+    role ffn_norm each branch has a norm of its own, x += mixer(norm(x)) + ffn(ffn_norm(x)), both of the
+    SAME x: both are taken before either branch adds into the stream (two RMS norms in one pass).
 
     In steps of single tokens the branches run side by side: such a step is a chain of
     short kernels that wait for one another, and the two branches meet only in the residual
@@ -157,9 +160,18 @@ class ParallelBlock(Block):
         self.norm = self.build(NORMS, "norm")
         self.mixer = self.build(MIXERS, "mixer")
         self.ffn = self.build(FEED_FORWARDS, "ffn") if "ffn" in layer_spec.parts else None
+        self.ffn_norm = self.build(NORMS, "ffn_norm") if self.ffn is not None and "ffn_norm" in layer_spec.parts \
+            else None
 
     def parts(self):
-        return tuple(p for p in (self.norm, self.mixer, self.ffn) if p is not None)
+        return tuple(p for p in (self.norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        # (a layer without a feed-forward has no use for its norm; a folder may still hold it)
+        for stem in self.spec.params.get("tolerated", ()):
+            specs.setdefault(f"{self.spec.prefix}.{stem}", WeightSpec((-1,), "unused"))
+        return specs
 
     def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
         n, width = hidden.shape
@@ -167,9 +179,21 @@ class ParallelBlock(Block):
         # (a buffer of its own: parts may use "normed" for their own rows)
         normed = ws.get("normed_parallel", (n, width), self.dtype)
         ctx.emit_for = None  # the next norm reads both branches' sum: no part may begin it
-        self.norm.forward(hidden, normed)
+        if self.ffn_norm is not None:
+            # the feed-forward's rows are made before the mixer adds into the stream they are taken from
+            normed_ffn = ws.get("normed_parallel_ffn", (n, width), self.dtype)
+            a, b = self.norm, self.ffn_norm
+            if getattr(a, "kind", None) == getattr(b, "kind", None) == "rmsnorm" and a.eps == b.eps:
+                ops.rmsnorm_pair(hidden, a.weight, b.weight, a.eps, normed, normed_ffn)
+            else:
+                a.forward(hidden, normed)
+                b.forward(hidden, normed_ffn)
+            mixer_in, normed = normed, normed_ffn
+        else:
+            self.norm.forward(hidden, normed)
+            mixer_in = normed
         if self.ffn is None:
-            self.mixer.forward(normed, ctx, hidden, cache)
+            self.mixer.forward(mixer_in, ctx, hidden, cache)
         elif self.SIDE_BY_SIDE and ctx.decode and width % 4 == 0:
             main = torch.cuda.current_stream()
             side = ws.stream("feed_forward")
@@ -182,11 +206,11 @@ class ParallelBlock(Block):
                 branch.zero_()
                 self.ffn.forward(normed, branch_ctx, branch)
                 join.record(side)
-            self.mixer.forward(normed, ctx, hidden, cache)
+            self.mixer.forward(mixer_in, ctx, hidden, cache)
             main.wait_event(join)
             ops.add_rows(hidden, branch)
         else:
-            self.mixer.forward(normed, ctx, hidden, cache)
+            self.mixer.forward(mixer_in, ctx, hidden, cache)
             self.ffn.forward(normed, ctx, hidden)
 
 

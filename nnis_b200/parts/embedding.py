@@ -57,12 +57,63 @@ class NormedTokenEmbedding(TokenEmbedding):
         self.norm.forward(hidden, hidden)
 
 
-class LinearHead(Part):
-    """params: vocab_size, hidden_size, name, tied_to (tensor stem or None), softcap
-    (0: none; else logits <- softcap * tanh(logits / softcap), which changes no greedy pick)."""
+class PairHashEmbedding(NormedTokenEmbedding):
+    """x = table[token] * scale + pair[row], then the norm: ``pair`` is a second table of
+    ``buckets`` + 1 rows, and a token's row is (token before * mul_prev + token * mul_cur) mod
+    buckets, the last row for a sequence's first token.  The token before is part of a sequence's
+    state: the embedding asks the cache for one int32 per slot, which holds the last token that
+    a step brought, so that a later portion or a single token finds it there.
+    params: vocab_size, hidden_size, name, norm, scale (1.0), and optionally pair {name, buckets,
+    mul_prev, mul_cur} (without it: the scaled embedding and the norm, no state)."""
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
+        self.scale = float(params.get("scale", 1.0))
+        pair = params.get("pair")
+        self.pair_name = self.tensor_name(pair["name"]) if pair else None
+        self.buckets = int(pair["buckets"]) if pair else 0
+        self.mul_prev = int(pair["mul_prev"]) if pair else 0
+        self.mul_cur = int(pair["mul_cur"]) if pair else 0
+        if pair and self.buckets <= 0:
+            raise ValueError("pair embedding: buckets must be positive")
+        self.pair_table: Optional[torch.Tensor] = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        specs = super().weight_specs()
+        if self.pair_name:
+            specs[self.pair_name] = WeightSpec((self.buckets + 1, self.width), "matrix")
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        if self.pair_name:
+            self.pair_table = tensors[self.pair_name]
+
+    def cache_request(self):
+        from ..cache import StateRequest
+        return StateRequest((1,), torch.int32) if self.pair_name else None
+
+    def forward(self, tokens: torch.Tensor, hidden: torch.Tensor, status: torch.Tensor) -> None:
+        raise RuntimeError("this embedding needs the step's context and its state: forward_step")
+
+    def forward_step(self, ctx, hidden: torch.Tensor, status: torch.Tensor, cache) -> None:
+        """The step's rows from ``ctx.tokens``; ``cache``: the view of the state asked for (None
+        without a pair table)."""
+        ops.embed_pair(self.table, self.pair_table, ctx.tokens, ctx.token_pos, ctx.token_seq, ctx.seq_slots,
+                       None if ctx.decode else ctx.seq_count, cache.state if cache is not None else None, hidden,
+                       status, self.scale, self.buckets, self.mul_prev, self.mul_cur)
+        self.norm.forward(hidden, hidden)
+
+
+class LinearHead(Part):
+    """params: vocab_size, hidden_size, name, tied_to (tensor stem or None), softcap
+    (0: none; else logits <- softcap * tanh(logits / softcap), which changes no greedy pick),
+    scale (1: none; the logits are multiplied by it, before a cap; a greedy pick is fused only
+    with a positive one)."""
+
+    def __init__(self, params, prefix, dtype, device):
+        super().__init__(params, prefix, dtype, device)
+        self.scale = float(params.get("scale", 1.0))
         self.softcap = float(params.get("softcap") or 0.0)
         self.vocab = int(params["vocab_size"])
         self.width = int(params["hidden_size"])
@@ -87,11 +138,13 @@ class LinearHead(Part):
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
         # (few rows: the decode projection kernel where it takes the shape)
         linear(x, self.weight, None, logits, STORE_F32, decode=True)
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
         if self.softcap:
             ops.softcap_rows(logits, self.softcap)
 
     def fuses_norm(self, norm, rows: int) -> bool:
-        return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16
+        return (getattr(norm, "kind", None) == "rmsnorm" and self.dtype == torch.bfloat16 and self.scale > 0
                 and rows <= ops.GEMV_HEAD_ROWS
                 and ops.gemv_takes(rows, self.vocab, self.width, ops.EPI_STORE_F32, self.device, True))
 
@@ -104,6 +157,8 @@ class LinearHead(Part):
         ops.gemv_bf16(self.weight, None, picks, ops.EPI_ARGMAX, hidden=hidden,
                       norm_weight=norm.weight, eps=norm.eps, rows=rows, m=picks.numel(),
                       logits=logits, scratch=scratch, next_tokens=next_tokens, next_pos=next_pos)
+        if self.scale != 1.0 and logits is not None:
+            ops.scale_rows(logits, self.scale)
         if self.softcap and logits is not None:
             ops.softcap_rows(logits, self.softcap)
 
@@ -115,10 +170,13 @@ class LinearHead(Part):
         """Final norm of the wanted rows folded into the head (few rows)."""
         ops.gemv_bf16(self.weight, None, logits, ops.EPI_STORE_F32, hidden=hidden,
                       norm_weight=norm.weight, eps=norm.eps, rows=rows, m=logits.shape[0])
+        if self.scale != 1.0:
+            ops.scale_rows(logits, self.scale)
         if self.softcap:
             ops.softcap_rows(logits, self.softcap)
 
 
 EMBEDDINGS.register("token_embedding", TokenEmbedding)
 EMBEDDINGS.register("normed_token_embedding", NormedTokenEmbedding)
+EMBEDDINGS.register("pair_hash_embedding", PairHashEmbedding)
 HEADS.register("linear_head", LinearHead)

@@ -136,9 +136,10 @@ class DenseMLP(Part):
     otherwise.
 
     params: hidden_size, intermediate_size, activation ("gelu": 0.5 z (1 + erf(z / sqrt 2));
-    "gelu_tanh": 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), names {up, down}."""
-    ACTIVATIONS = {"gelu": ops.GELU_ERF, "gelu_tanh": ops.GELU_TANH}
-    FUSED = {ops.GELU_ERF: ops.GEMM_ACT_GELU_ERF, ops.GELU_TANH: ops.GEMM_ACT_GELU_TANH}  # the products' codes
+    "gelu_tanh": 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))); "relu2": max(z, 0)^2), names {up, down}."""
+    ACTIVATIONS = {"gelu": ops.GELU_ERF, "gelu_tanh": ops.GELU_TANH, "relu2": ops.RELU2}
+    FUSED = {ops.GELU_ERF: ops.GEMM_ACT_GELU_ERF, ops.GELU_TANH: ops.GEMM_ACT_GELU_TANH,
+             ops.RELU2: ops.GEMM_ACT_RELU2}  # the products' codes
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)

@@ -25,10 +25,20 @@ Prompt steps in bfloat16 sort the pairs by expert and run grouped products: on m
 (score and activation in the first product's epilogue) where an expert gets few rows, on the
 tcgen05 kernel (float32 sums, then a row-wise kernel for score and activation) where it gets many.
 
+A third form (``scores`` "softmax_all" with gated experts and ``weight_on`` "output"): the scores
+are ONE softmax over all the router's outputs; the choice goes by score + a stored correction per
+output (``names["correction"]``), group by group (``groups`` equal runs of neighbouring outputs, a
+run's score its largest corrected score, only the ``keep`` best runs can be chosen), and the chosen
+scores weigh the experts' OUTPUTS as they are, not renormalised.  The router's last ``identity``
+outputs have no matrices: such an expert hands its input on, so the token's output takes weight *
+h from it.  The shared expert of this form is a gated feed-forward of its own (``shared``: a
+``gated_mlp`` PartSpec) that runs for every token.
+
 params: hidden_size, experts, top, ff, shared_ff (0: no shared expert), activation
-("relu2" | "silu_gated"), scores ("softmax" over the chosen logits | "sigmoid"), weight_on
-("output" | "input"), names {router, router_bias (optional), expert (a format with {e}), up,
-down, gate (gated experts), shared_up, shared_down, shared_gate}.
+("relu2" | "silu_gated"), scores ("softmax" over the chosen logits | "sigmoid" | "softmax_all"),
+weight_on ("output" | "input"), identity, groups, keep, shared (a PartSpec), names {router,
+router_bias (optional), correction (optional), expert (a format with {e}), up, down, gate (gated
+experts), shared_up, shared_down, shared_gate}.
 """
 from __future__ import annotations
 
@@ -39,6 +49,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import WeightSpec
 from .base import FEED_FORWARDS, Part
+from .mlp import GatedMLP
 from .linear import ADD_F32, STORE_F32, linear
 
 
@@ -57,15 +68,30 @@ class MoEFeedForward(Part):
         self.activation = params.get("activation", "relu2")
         self.scores = params.get("scores", "softmax")
         self.weight_on = params.get("weight_on", "output")
+        self.identity = int(params.get("identity") or 0)
+        self.groups = int(params.get("groups") or 1)
+        self.keep = int(params.get("keep") or self.groups)
+        self.by_choice = self.scores == "softmax_all"
         if (self.activation, self.scores, self.weight_on) not in (("relu2", "softmax", "output"),
-                                                                  ("silu_gated", "sigmoid", "input")):
+                                                                  ("silu_gated", "sigmoid", "input"),
+                                                                  ("silu_gated", "softmax_all", "output")):
             raise ValueError(f"moe: no kernel for activation {self.activation!r} with {self.scores!r} scores "
                              f"on the expert's {self.weight_on}")
         self.gated = self.activation == "silu_gated"
         if self.gated and self.shared_ff:
-            raise ValueError("moe: the gated form has no shared expert")
-        if not 0 < self.top <= self.experts:
-            raise ValueError(f"moe: top={self.top} of {self.experts} experts")
+            raise ValueError("moe: the gated form's shared expert is a part of its own (shared)")
+        self.outputs = self.experts + self.identity  # of the router
+        if not self.by_choice and (self.identity or self.groups != 1 or params.get("shared") is not None):
+            raise ValueError("moe: identity experts, groups and a shared part go with softmax_all scores")
+        if not 0 < self.top <= self.outputs:
+            raise ValueError(f"moe: top={self.top} of {self.outputs} experts")
+        if self.groups <= 0 or self.outputs % self.groups or not 0 < self.keep <= self.groups \
+                or self.top > self.keep * (self.outputs // self.groups):
+            raise ValueError(f"moe: {self.groups} groups (keep {self.keep}) over {self.outputs} router outputs "
+                             f"with top={self.top}")
+        shared = params.get("shared")
+        self.shared = GatedMLP(shared.params, prefix, dtype, device) if shared is not None else None
+        self.correction = None
         self.w_router = self.b_router = self.w_up = self.w_down = None
         self.w_shared_up = self.w_shared_down = None
 
@@ -75,7 +101,11 @@ class MoEFeedForward(Part):
     def weight_specs(self) -> Dict[str, WeightSpec]:
         W = self.hidden
         # the router is held in float32 whatever the operand dtype ("vector": kept as float32)
-        specs = {self.tensor_name(self.names["router"]): WeightSpec((self.experts, W), "vector", fan_in=W)}
+        specs = {self.tensor_name(self.names["router"]): WeightSpec((self.outputs, W), "vector", fan_in=W)}
+        if self.names.get("correction"):
+            specs[self.tensor_name(self.names["correction"])] = WeightSpec((self.outputs,), "vector")
+        if self.shared is not None:
+            specs.update(self.shared.weight_specs())
         if self.names.get("router_bias"):
             specs[self.tensor_name(self.names["router_bias"])] = WeightSpec((self.experts,), "vector")
         for e in range(self.experts):
@@ -94,6 +124,10 @@ class MoEFeedForward(Part):
         self.w_router = tensors[self.tensor_name(self.names["router"])]
         self.b_router = tensors[self.tensor_name(self.names["router_bias"])] \
             if self.names.get("router_bias") else None
+        self.correction = tensors[self.tensor_name(self.names["correction"])] \
+            if self.names.get("correction") else None
+        if self.shared is not None:
+            self.shared.load(tensors)
         if self.gated:  # per expert, row 2f the gate's and row 2f + 1 the up-projection's of feature f
             self.w_up = torch.stack([torch.stack([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], 1)
                                      .reshape(2 * self.ff, self.hidden) for e in range(self.experts)]).contiguous()
@@ -114,6 +148,8 @@ class MoEFeedForward(Part):
         per_expert = (3 if self.gated else 2) * self.ff * self.hidden * self.w_up.element_size()
         shared = sum(t.numel() * t.element_size() for t in (self.w_shared_up, self.w_shared_down)
                      if t is not None)
+        if self.shared is not None:
+            shared += self.shared.parameter_bytes()
         return self.w_router.numel() * 4 + self.top * per_expert + shared
 
     def step_bytes(self, rows: int) -> int:
@@ -126,15 +162,19 @@ class MoEFeedForward(Part):
 
     def step_flops(self, counts, starts) -> float:
         W = self.hidden
-        per_token = W * self.experts + (3 if self.gated else 2) * self.top * self.ff * W \
+        per_token = W * self.outputs + (3 if self.gated else 2) * self.top * self.ff * W \
             + self.shared_ff * (2 * W + 1) + W
-        return 2.0 * sum(counts) * per_token
+        shared = self.shared.step_flops(counts, starts) if self.shared is not None else 0.0
+        return 2.0 * sum(counts) * per_token + shared
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         n = residual.shape[0]
         ws = ctx.workspace
         ids = ws.get("moe_ids", (n, self.top), torch.int32)
         weights = ws.get("moe_weights", (n, self.top), torch.float32)
+        if self.by_choice:
+            self._forward_by_choice(x, ctx, residual, ids, weights)
+            return
         ops.moe_route(x, self.w_router, self.b_router, ctx.token_pos, ids, weights, self.top,
                       sigmoid_scores=self.scores == "sigmoid")
         grouped_gated = self.gated and self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM \
@@ -196,6 +236,20 @@ class MoEFeedForward(Part):
             shared_act = ws.get("moe_shared_act", (n, self.shared_ff), self.dtype)
             ops.relu2_gate(up, shared_act)
             linear(shared_act, self.w_shared_down, None, residual, ADD_F32, ws, decode=ctx.decode)
+
+
+    def _forward_by_choice(self, x, ctx, residual, ids, weights) -> None:
+        """The form whose scores are one softmax over all outputs (see the module's text)."""
+        n = residual.shape[0]
+        ws = ctx.workspace
+        passed = ws.get("moe_pass_weight", (n,), torch.float32)
+        ops.moe_route_choice(x, self.w_router, self.correction, ctx.token_pos, ids, weights, passed, self.experts,
+                             self.top, self.groups, self.keep)
+        act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
+        ops.moe_experts_gated_out(x, self.w_up, self.w_down, ids, weights, passed if self.identity else None,
+                                  ctx.token_pos, act, residual, self.top)
+        if self.shared is not None:
+            self.shared.forward(x, ctx, residual)
 
 
 FEED_FORWARDS.register("moe", MoEFeedForward)

@@ -11,21 +11,26 @@ from .base import NORMS, Part
 
 
 class RMSNorm(Part):
-    """params: size, eps, name (tensor stem)."""
+    """params: size, eps, name (tensor stem), and optionally ``offset``: the stored tensor w lies
+    around zero and the multiplier is offset + w (added once at load, in float32, so every kernel
+    that takes this norm's weight, alone or folded into a projection, serves it unchanged)."""
     kind = "rmsnorm"  # parts that can fold this norm into their first projection look for it
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.offset = float(params.get("offset") or 0.0)
         self.name = self.tensor_name(params["name"])
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.name: WeightSpec((self.size,), "vector", init="ones")}
+        return {self.name: WeightSpec((self.size,), "vector", init="normal" if self.offset else "ones")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name]
+        if self.offset:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
 
     def parameter_bytes(self) -> int:
         return self.size * 4

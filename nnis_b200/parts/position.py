@@ -50,8 +50,15 @@ class RotaryFrequencies(PositionEncoding):
     and ``scaling`` {factor, low, high, original}: frequencies whose wavelength 2 pi / f
     exceeds original / low are divided by ``factor``, those with a wavelength below
     original / high stay, and between the two the frequency is (1 - s) f / factor + s f
-    with s = (original / wavelength - low) / (high - low).  Mixers whose kernels take
-    frequencies (latent attention, retention, attention with a sink) ask for ``frequencies()``."""
+    with s = (original / wavelength - low) / (high - low).  A second form of ``scaling``,
+    {ramp: "index", factor, original, fast, slow}, blends by the INDEX of a frequency: with
+    at(t) = dims * ln(original / (2 pi t)) / (2 ln base), the index whose wavelength makes t turns
+    over ``original`` positions, lo = max(floor(at(fast)), 0), hi = min(ceil(at(slow)), dims - 1) and
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is r_i f_i / factor +
+    (1 - r_i) f_i, and every cosine and sine is multiplied by ``magnitude`` = 0.1 ln(factor) + 1
+    (a mixer's kernel has to apply it; 1.0 for every other form).  Mixers whose kernels take
+    frequencies (latent attention, retention, attention with a sink, differential attention) ask
+    for ``frequencies()``."""
 
     def __init__(self, params, prefix, dtype, device):
         super().__init__(params, prefix, dtype, device)
@@ -63,12 +70,32 @@ class RotaryFrequencies(PositionEncoding):
             raise ValueError(f"rotation: dims={self.dims} must be even")
         if self.pairing not in ("half", "neighbours"):
             raise ValueError(f"rotation: pairing {self.pairing!r} is not known (half, neighbours)")
-        if self.scaling is not None:
+        self.by_index = self.scaling is not None and self.scaling.get("ramp") == "index"
+        self.magnitude = 1.0
+        if self.by_index:
+            sc = self.scaling
+            if not all(float(sc[k]) > 0 for k in ("factor", "original", "fast", "slow")) or self.base <= 1.0:
+                raise ValueError("rotation: the ramp over indices needs positive factor, original, fast, slow "
+                                 "and a base above 1")
+            self.magnitude = 0.1 * math.log(float(sc["factor"])) + 1.0
+        elif self.scaling is not None:
             sc = self.scaling
             if not all(float(sc[k]) > 0 for k in ("factor", "low", "high", "original")) \
                     or float(sc["high"]) == float(sc["low"]):
                 raise ValueError("rotation: scaling needs positive factor, low, high, original and low != high")
         self._freq: Optional[torch.Tensor] = None
+
+    def _ramped(self, freq: torch.Tensor) -> torch.Tensor:
+        sc = self.scaling
+        factor, original = float(sc["factor"]), float(sc["original"])
+
+        def at(turns: float) -> float:
+            return self.dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+        lo = max(math.floor(at(float(sc["fast"]))), 0)
+        hi = min(math.ceil(at(float(sc["slow"]))), self.dims - 1)
+        f = freq.to(torch.float64)
+        ramp = torch.clamp((torch.arange(f.numel(), dtype=torch.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return (f / factor * ramp + f * (1.0 - ramp)).to(torch.float32)
 
     def _scaled(self, freq: torch.Tensor) -> torch.Tensor:
         sc = self.scaling
@@ -84,9 +111,10 @@ class RotaryFrequencies(PositionEncoding):
         if self._freq is None:
             half = self.dims // 2
             exponent = -(2 * torch.arange(half, dtype=torch.float64)) / float(max(self.dims, 1))
-            freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), exponent).to(torch.float32)
+            freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), exponent)
             if self.scaling is not None and half:
-                freq = self._scaled(freq)
+                freq = self._ramped(freq) if self.by_index else self._scaled(freq.to(torch.float32))
+            freq = freq.to(torch.float32)
             # (one spare entry so that dims == 0 still has an address)
             self._freq = torch.cat([freq, torch.zeros(1)]).to(self.device).contiguous()
         return self._freq
