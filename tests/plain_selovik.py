@@ -202,3 +202,14 @@ def forward(tokens: List[int], w: Dict[str, torch.Tensor], cfg: dict, emulate_bf
             layers_out.append(x.clone())
     h = bf(centred_norm(x, w["final.norm"], eps), e16)
     return (h @ w["embed"].to(F).T) * float(cfg.get("logit_scale", 1.0))
+
+
+def greedy_generate(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    """n tokens, each the largest logit after everything so far (ties to the lower id)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        logits = forward(seq, w, cfg)[-1]
+        t = int(torch.nonzero(logits == logits.max())[0])
+        out.append(t)
+        seq.append(t)
+    return out
