@@ -25,7 +25,7 @@ DTYPES = ["float32", "bfloat16"]
 F = torch.float64
 # a router's choice between two experts whose corrected scores lie closer than this may go either way
 # in bfloat16 (the scores are probabilities); such positions are left out, and they must be few
-CLOSE_CALL = 0.01
+CLOSE_CALL = 0.002
 
 
 @pytest.fixture(scope="module")
