@@ -41,7 +41,8 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_t
     for (int e = tid; e < experts; e += 1024) count[e] = cursor[e] = 0;
     for (int p = tid; p < max_tiles * tile_rows; p += 1024) perm[p] = -1;
     __syncthreads();
-    for (int p = tid; p < n_pairs; p += 1024) atomicAdd(&count[ids[p]], 1);
+    for (int p = tid; p < n_pairs; p += 1024)
+        if (ids[p] >= 0) atomicAdd(&count[ids[p]], 1);  // (a negative id: a pair without an expert)
     __syncthreads();
     if (tid == 0) {
         int at = 0;
@@ -67,6 +68,10 @@ moe_sort_kernel(const int* __restrict__ ids, int n_pairs, int experts, int max_t
     }
     for (int p = tid; p < n_pairs; p += 1024) {
         int e = ids[p];
+        if (e < 0) {
+            place[p] = -1;
+            continue;
+        }
         int at = first[e] + atomicAdd(&cursor[e], 1);
         perm[at] = p;
         place[p] = at;
@@ -100,7 +105,7 @@ grouped_mma_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ 
         } else {
             int p = perm[row0 + tid];
             src_row[tid] = (MODE == 0 || MODE == 3) ? (p < 0 ? -1 : p / top) : (p < 0 ? -1 : row0 + tid);
-            if (MODE == 3) row_weight[tid] = p < 0 ? 0.f : pair_weight[p];
+            if (MODE == 3) row_weight[tid] = p < 0 ? 0.f : (pair_weight ? pair_weight[p] : 1.0f);
         }
     }
     __syncthreads();
@@ -206,7 +211,7 @@ moe_gated_act_kernel(const float* __restrict__ up, const int* __restrict__ perm,
     pdl_launch_dependents();
     const long long row = blockIdx.x;
     const int p = perm[row];
-    const float s = p < 0 ? 0.f : weights[p];
+    const float s = p < 0 ? 0.f : (weights ? weights[p] : 1.0f);
     const float2* in = reinterpret_cast<const float2*>(up + (size_t)row * 2 * ff);
     for (int f = threadIdx.x; f < ff; f += 256) {
         float2 gu = in[f];
@@ -217,11 +222,14 @@ moe_gated_act_kernel(const float* __restrict__ up, const int* __restrict__ perm,
 
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place,
-                   const float* __restrict__ weights, float* __restrict__ residual, int width, int top) {
+                   const float* __restrict__ weights, float* __restrict__ residual, int width, int top,
+                   const float* __restrict__ pass_weight, const bf16* __restrict__ x) {
     const long long n = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += 256) {
-        float sum = 0.f;
+        // (pairs without an expert hand the token's input on: their weights' sum times the input)
+        float sum = pass_weight ? pass_weight[n] * to_float(x[(size_t)n * width + c]) : 0.f;
         for (int s = 0; s < top; ++s) {
+            if (place[n * top + s] < 0) continue;
             float v = y[(size_t)place[n * top + s] * width + c];
             sum = weights ? fmaf(weights[n * top + s], v, sum) : sum + v;
         }
@@ -307,16 +315,20 @@ NNIS_API int nnis_moe_grouped(const void* x, const void* w_up, const void* w_dow
         (const bf16*)x, width, perm, top, (const bf16*)w_up, tile_expert, act, ff, width, 0, 0, 0, 0);
     grouped_mma_kernel<1><<<dim3(tiles, (width + 63) / 64), 128, smem, stream>>>(
         (const bf16*)act, ff, perm, top, (const bf16*)w_down, tile_expert, y, width, ff, 0, 0, 0, 0);
-    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top,
+                                                     (const float*)nullptr, (const bf16*)nullptr);
     NNIS_RETURN_LAUNCH();
 }
 
 // Gated experts with the scores on their inputs: w_gu [experts, 2 ff, width] with the gate's and
-// the up-projection's rows interleaved; the rest as nnis_moe_grouped (act [tiles * 64, ff]).
+// the up-projection's rows interleaved; the rest as nnis_moe_grouped (act [tiles * 64, ff]).  With
+// `weight_on_output` the scores weigh the experts' outputs instead (in the combine step), a pair with a
+// negative id has no expert and takes no row, and pass_weight (float32 [n_tokens] or null) times the
+// token's input is added.
 NNIS_API int nnis_moe_grouped_gated(const void* x, const void* w_gu, const void* w_down, const int* ids,
                                     const float* weights, int* perm, int* place, int* tile_expert, void* act,
                                     float* y, float* residual, int n_tokens, int width, int ff, int experts,
-                                    int top, cudaStream_t stream) {
+                                    int top, int weight_on_output, const float* pass_weight, cudaStream_t stream) {
     if (n_tokens <= 0 || top <= 0 || !x || !w_gu || !w_down || !ids || !weights || !perm || !place ||
         !tile_expert || !act || !y || !residual)
         return NNIS_ERR_ARGUMENT;
@@ -329,10 +341,13 @@ NNIS_API int nnis_moe_grouped_gated(const void* x, const void* w_gu, const void*
     int code = configure_grouped();
     if (code != NNIS_OK) return code;
     grouped_mma_kernel<3><<<dim3(tiles, (2 * ff + 63) / 64), 128, kGroupedSmem, stream>>>(
-        (const bf16*)x, width, perm, top, (const bf16*)w_gu, tile_expert, act, 2 * ff, width, 0, 0, 0, 0, weights);
+        (const bf16*)x, width, perm, top, (const bf16*)w_gu, tile_expert, act, 2 * ff, width, 0, 0, 0, 0,
+        weight_on_output ? (const float*)nullptr : weights);
     grouped_mma_kernel<1><<<dim3(tiles, (width + 63) / 64), 128, kGroupedSmem, stream>>>(
         (const bf16*)act, ff, perm, top, (const bf16*)w_down, tile_expert, y, width, ff, 0, 0, 0, 0);
-    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, (const float*)nullptr, residual, width, top);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weight_on_output ? weights : (const float*)nullptr,
+                                                     residual, width, top, weight_on_output ? pass_weight : nullptr,
+                                                     (const bf16*)x);
     NNIS_RETURN_LAUNCH();
 }
 
@@ -371,7 +386,8 @@ NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_
     code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, 0, sm_count, status, pdl,
                                 stream);
     if (code != NNIS_OK) return code;
-    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weights, residual, width, top,
+                                                     (const float*)nullptr, (const bf16*)nullptr);
     NNIS_RETURN_LAUNCH();
 }
 
@@ -381,7 +397,8 @@ NNIS_API int nnis_moe_grouped_tc(const void* x, const void* w_up, const void* w_
 NNIS_API int nnis_moe_grouped_gated_tc(const void* x, const void* w_gu, const void* w_down, const int* ids,
                                        const float* weights, int* perm, int* place, int* tile_expert,
                                        void* x_sorted, float* up, void* act, float* y, float* residual,
-                                       int n_tokens, int width, int ff, int experts, int top, int sm_count,
+                                       int n_tokens, int width, int ff, int experts, int top,
+                                       int weight_on_output, const float* pass_weight, int sm_count,
                                        int* status, int pdl, cudaStream_t stream) {
     if (n_tokens <= 0 || top <= 0 || !x || !w_gu || !w_down || !ids || !weights || !perm || !place ||
         !tile_expert || !x_sorted || !up || !act || !y || !residual)
@@ -400,11 +417,13 @@ NNIS_API int nnis_moe_grouped_gated_tc(const void* x, const void* w_gu, const vo
                                     pdl, stream);
     if (code != NNIS_OK) return code;
     e = launch_dependent(moe_gated_act_kernel, (unsigned)rows, 256, 0, stream, (const float*)up, (const int*)perm,
-                         weights, (bf16*)act, ff);
+                         weight_on_output ? (const float*)nullptr : weights, (bf16*)act, ff);
     if (e != cudaSuccess) return (int)e;
     code = nnis_gemm_tc_grouped(act, w_down, y, rows, width, ff, experts, tile_expert, 0, sm_count, status, pdl,
                                 stream);
     if (code != NNIS_OK) return code;
-    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, (const float*)nullptr, residual, width, top);
+    moe_combine_kernel<<<n_tokens, 256, 0, stream>>>(y, place, weight_on_output ? weights : (const float*)nullptr,
+                                                     residual, width, top, weight_on_output ? pass_weight : nullptr,
+                                                     (const bf16*)x);
     NNIS_RETURN_LAUNCH();
 }

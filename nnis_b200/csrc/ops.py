@@ -1674,7 +1674,8 @@ def moe_experts_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
 
 def moe_grouped_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                       weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
-                      act: torch.Tensor, y: torch.Tensor, residual: torch.Tensor, top: int) -> None:
+                      act: torch.Tensor, y: torch.Tensor, residual: torch.Tensor, top: int, on_output: bool = False,
+                      pass_weight: Optional[torch.Tensor] = None) -> None:
     """``moe_experts_gated`` for many tokens in bfloat16: the pairs sorted by expert in runs padded to 64
     rows, two grouped products on mma.sync tiles (the first with the gated activation and the score in
     its epilogue), then the plain sum of each token's experts.  Scratch as ``moe_grouped``."""
@@ -1692,17 +1693,20 @@ def moe_grouped_gated(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
     _need(residual.dtype == torch.float32 and tuple(residual.shape) == (n, width), "moe_grouped_gated: residual")
     _check(_lib().nnis_moe_grouped_gated(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
                                          _ptr(place), _ptr(tile_expert), _ptr(act), _ptr(y), _ptr(residual), n, width,
-                                         ff, experts, top, _stream()), "moe_grouped_gated", 4)
+                                         ff, experts, top, 1 if on_output else 0, _ptr(pass_weight), _stream()),
+           "moe_grouped_gated", 4)
 
 
 def moe_grouped_gated_tc(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor,
                          weights: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile_expert: torch.Tensor,
                          x_sorted: torch.Tensor, up: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
-                         residual: torch.Tensor, top: int) -> None:
+                         residual: torch.Tensor, top: int, on_output: bool = False,
+                         pass_weight: Optional[torch.Tensor] = None) -> None:
     """``moe_grouped_gated`` with both products on the tcgen05 kernel: runs padded to tiles of 128 rows
     (``moe_grouped_tc_tiles``); ``up`` float32 [tiles * 128, 2 ff] takes the first product's sums, a row-wise
-    kernel applies score and activation."""
-    _cuda(h, w_gu, w_down, ids, weights, perm, place, tile_expert, x_sorted, up, act, y, residual)
+    kernel applies score and activation.  ``on_output``: the scores weigh the experts' outputs instead, a
+    negative id has no expert, and ``pass_weight`` [n] times the token's input is added."""
+    _cuda(h, w_gu, w_down, ids, weights, perm, place, tile_expert, x_sorted, up, act, y, residual, pass_weight)
     n, width = h.shape
     experts, ff2, _ = w_gu.shape
     ff = ff2 // 2
@@ -1720,6 +1724,7 @@ def moe_grouped_gated_tc(h: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tens
     _check(_lib().nnis_moe_grouped_gated_tc(_ptr(h), _ptr(w_gu), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(perm),
                                             _ptr(place), _ptr(tile_expert), _ptr(x_sorted), _ptr(up), _ptr(act),
                                             _ptr(y), _ptr(residual), n, width, ff, experts, top,
+                                            1 if on_output else 0, _ptr(pass_weight),
                                             sm_count(h.device), _ptr(status_word(h.device)), PDL, _stream()),
            "moe_grouped_gated_tc", 6)
 
@@ -1966,4 +1971,29 @@ DIFF_MMA = 0 if os.environ.get("NNIS_DIFF_MMA", "1") == "0" else 1
 def attention_diff_mma_takes(dk: int, dv: int, page_size: int) -> bool:
     """Whether the tensor-core prompt form of differential attention takes maps of ``dk`` values and
     values of ``dv``."""
-    return False
+    return bool(DIFF_MMA) and dk in (32, 64, 128) and dv in (64, 128) and page_size == 64
+
+
+def attention_diff_mma(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles: torch.Tensor,
+                       seq_first_row: torch.Tensor, seq_start: torch.Tensor, seq_count: torch.Tensor,
+                       page_table: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, heads: int,
+                       kv_heads: int, window: int, scale: float, lam: float, post: float, eps: float) -> None:
+    """``attention_diff`` for prompt steps in bfloat16 on mma.sync tiles; ``tiles`` int32 [n, 2] =
+    (sequence, first query) per 64 queries."""
+    _cuda(q, k_cache, v_cache, tiles, seq_first_row, seq_start, seq_count, page_table, gate, out)
+    pages, nkv, page_size, dk2 = k_cache.shape
+    dv = v_cache.shape[3]
+    n = out.shape[0]
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype == torch.bfloat16, "attention_diff_mma: bfloat16")
+    _need(attention_diff_mma_takes(dk2 // 2, dv, page_size) and nkv == kv_heads and dk2 % 2 == 0,
+          "attention_diff_mma: maps of 32, 64 or 128, values of 64 or 128, pages of 64")
+    _need(tuple(q.shape) == (n, heads * dk2) and tuple(out.shape) == (n, heads * dv),
+          "attention_diff_mma: q [n, heads * 2 dk], out [n, heads * dv]")
+    _need(tiles.dtype == torch.int32 and tiles.dim() == 2 and tiles.shape[1] == 2, "attention_diff_mma: tiles [n, 2]")
+    _need(gate is None or (gate.dtype == torch.float32 and tuple(gate.shape) == (n, heads * dv)),
+          "attention_diff_mma: gate float32 [n, heads * dv]")
+    _check(_lib().nnis_attention_diff_mma(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(tiles), tiles.shape[0],
+                                          _ptr(seq_first_row), _ptr(seq_start), _ptr(seq_count), _ptr(page_table),
+                                          page_table.shape[1], _ptr(gate), _ptr(out), heads, kv_heads, dk2 // 2, dv,
+                                          page_size, window, ctypes.c_float(scale), ctypes.c_float(lam),
+                                          ctypes.c_float(post), ctypes.c_float(eps), _stream()), "attention_diff_mma")

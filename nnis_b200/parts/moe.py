@@ -245,9 +245,34 @@ class MoEFeedForward(Part):
         passed = ws.get("moe_pass_weight", (n,), torch.float32)
         ops.moe_route_choice(x, self.w_router, self.correction, ctx.token_pos, ids, weights, passed, self.experts,
                              self.top, self.groups, self.keep)
-        act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
-        ops.moe_experts_gated_out(x, self.w_up, self.w_down, ids, weights, passed if self.identity else None,
-                                  ctx.token_pos, act, residual, self.top)
+        pass_weight = passed if self.identity else None
+        grouped = self.dtype == torch.bfloat16 and not ctx.decode and n >= self.GROUPED_FROM and ops.MOE_GROUPED \
+            and ops.moe_grouped_takes(self.hidden, self.ff, self.experts)
+        if grouped and ops.TC_GEMM and n * self.top >= self.TCGEN05_ROWS * self.experts:
+            # many tokens an expert: runs padded to 128 rows, both products on the tcgen05 kernel
+            tiles = ops.moe_grouped_tc_tiles(n * self.top, self.experts)
+            ops.moe_grouped_gated_tc(x, self.w_up, self.w_down, ids, weights,
+                                     ws.get("moe_perm", (tiles * 128,), torch.int32),
+                                     ws.get("moe_place", (n * self.top,), torch.int32),
+                                     ws.get("moe_tile_expert", (tiles,), torch.int32),
+                                     ws.get("moe_x_sorted", (tiles * 128, self.hidden), self.dtype),
+                                     ws.get("moe_up_sorted", (tiles * 128, 2 * self.ff), torch.float32),
+                                     ws.get("moe_act_sorted", (tiles * 128, self.ff), self.dtype),
+                                     ws.get("moe_y_sorted", (tiles * 128, self.hidden), torch.float32), residual,
+                                     self.top, on_output=True, pass_weight=pass_weight)
+        elif grouped:
+            tiles = ops.moe_grouped_tiles(n * self.top, self.experts)
+            ops.moe_grouped_gated(x, self.w_up, self.w_down, ids, weights,
+                                  ws.get("moe_perm", (tiles * 64,), torch.int32),
+                                  ws.get("moe_place", (n * self.top,), torch.int32),
+                                  ws.get("moe_tile_expert", (tiles,), torch.int32),
+                                  ws.get("moe_act_sorted", (tiles * 64, self.ff), self.dtype),
+                                  ws.get("moe_y_sorted", (tiles * 64, self.hidden), torch.float32), residual,
+                                  self.top, on_output=True, pass_weight=pass_weight)
+        else:
+            act = ws.get("moe_act", (n, self.top, self.ff), self.dtype)
+            ops.moe_experts_gated_out(x, self.w_up, self.w_down, ids, weights, pass_weight, ctx.token_pos, act,
+                                      residual, self.top)
         if self.shared is not None:
             self.shared.forward(x, ctx, residual)
 

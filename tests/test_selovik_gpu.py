@@ -280,6 +280,50 @@ def test_attention_with_two_maps_in_every_cut(H, G, dk, dv, window):
         assert torch.allclose(out[[0, 2]].cpu().double(), (want / gate.double())[[150, 151]], atol=tol, rtol=tol)
 
 
+@pytest.mark.parametrize("H, G, dk, dv, window", [(4, 2, 32, 64, 100), (2, 1, 32, 128, 70), (6, 2, 64, 64, 0), (3, 3, 64, 128, 64),
+                                                  (2, 2, 128, 128, 129), (4, 1, 128, 64, 65)])
+def test_prompt_attention_on_the_tensor_cores(H, G, dk, dv, window):
+    """The tensor-core prompt form against plain float64 and against the any-size kernel: two sequences in one
+    step, one of them a later portion that starts inside a page, tiles that end inside a page."""
+    from nnis_b200.csrc import ops
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(H * 1000 + dk + dv)
+    lam, post, eps, scale = 0.8, 0.5, 1e-5, 1.2 / math.sqrt(dk)
+    lens, starts = [230, 150], [0, 75]       # the second sequence already holds 75 positions
+    counts = [lens[0], lens[1] - starts[1]]
+    pages = [[3, 0, 6, 1], [2, 7, 5]]
+    k_cache = torch.full((8, G, 64, 2 * dk), 50.0, dtype=torch.bfloat16)
+    v_cache = torch.full((8, G, 64, dv), -50.0, dtype=torch.bfloat16)
+    qs, want = [], []
+    for i, n in enumerate(lens):
+        q = torch.randn(n, H, 2, dk, generator=g).bfloat16()
+        k = torch.randn(n, G, 2, dk, generator=g).bfloat16()
+        v = torch.randn(n, G, dv, generator=g).bfloat16()
+        gate = torch.rand(n, H * dv, generator=g)
+        for t in range(n):
+            k_cache[pages[i][t // 64], :, t % 64] = k[t].reshape(G, 2 * dk)
+            v_cache[pages[i][t // 64], :, t % 64] = v[t]
+        full = _plain_two_maps(q.double(), k.double(), v.double(), window, scale, lam, post, eps, gate.double())
+        qs.append((q[starts[i]:].reshape(counts[i], -1), gate[starts[i]:]))
+        want.append(full[starts[i]:])
+    q = torch.cat([a for a, _ in qs]).to(dev)
+    gate = torch.cat([b for _, b in qs]).to(dev)
+    want = torch.cat(want)
+    table = torch.tensor([pages[0], pages[1] + [-1]], dtype=torch.int32, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    tiles = i32([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, 64)])
+    out = torch.full((sum(counts), H * dv), 9.0, dtype=torch.bfloat16, device=dev)
+    assert ops.attention_diff_mma_takes(dk, dv, 64)
+    ops.attention_diff_mma(q, k_cache.to(dev), v_cache.to(dev), tiles, i32([0, counts[0]]), i32(starts), i32(counts), table,
+                           gate, out, H, G, window, scale, lam, post, eps)
+    assert torch.allclose(out.cpu().double(), want, atol=3e-2, rtol=3e-2)
+    pos = i32(list(range(lens[0])) + list(range(starts[1], lens[1])))
+    seq = i32([0] * counts[0] + [1] * counts[1])
+    other = torch.empty_like(out)
+    ops.attention_diff(q, k_cache.to(dev), v_cache.to(dev), pos, seq, table, gate, other, H, G, window, scale, lam, post, eps)
+    assert torch.allclose(out.float(), other.float(), atol=3e-2, rtol=3e-2)
+
+
 def test_rotation_of_every_map_before_the_cache():
     """qkv_prep with two maps a head: each map's first values turned by itself, the magnitude on
     cosine and sine, keys into the cache row, the gates' sigmoid."""
