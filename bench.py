@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 135m|360m|1.7b] [--batch B] [--context C] [--layers L] [--skip-points]
-                    [--skip-e2e] [--designs s,m [--only-design llama,nafezen,tazadra,sedopel]]
+                    [--skip-e2e] [--designs s,m [--only-design llama,nafezen,tazadra,sedopel,selovik]]
 
 A step is one decode step of a batch of 8 sequences whose context ends at 4,096
 tokens (prompt 2,048 + 2,048 decoded); ``value`` is decoded tokens per second,
@@ -236,16 +236,18 @@ def timeline(engine, batch, path, rng, vocab):
 
 
 # ---------------------------------------------------------------------------
-# --designs: the Nafezen, Tazadra and Sedopel designs beside the Llama decoder at equal width and depth
+# --designs: the Nafezen, Tazadra, Sedopel and Selovik designs beside the Llama decoder at equal width and depth
 # ---------------------------------------------------------------------------
 def design_configs(size: str):
-    """(Llama, Nafezen, Tazadra, Sedopel) configurations of one width, depth, vocabulary and dense
+    """(Llama, Nafezen, Tazadra, Sedopel, Selovik) configurations of one width, depth, vocabulary and dense
     feed-forward size; the Nafezen layers alternate latent attention with dense and expert
     feed-forwards and hold one retention layer in four; the Tazadra layers are attention with a
     sink + dense, WKV + experts, selective scan + experts, and attention that reads the first
     layer's keys + dense, twice; the Sedopel layers alternate a pair of mixers (gated softmax
     attention beside lightning attention) + dense with the gated delta rule, which has a dense
-    feed-forward every other time."""
+    feed-forward every other time; the Selovik layers are differential attention (two maps of half a
+    head's size over values of a head's size, a window of 1,024) with dense and expert feed-forwards
+    in turn, six layers of which the second and third run twice (eight layer runs)."""
     width, heads, ff, layers, q_rank, kv_rank, experts, top = {
         "s": (1024, 16, 2816, 8, 384, 256, 16, 2),
         "m": (2048, 16, 5632, 8, 768, 512, 32, 4),
@@ -294,10 +296,22 @@ def design_configs(size: str):
                             ("parallel", {"left": softmax, "right": lightning}, dense), ("delta", delta, None)][i % 4]
         s_layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
     sedopel = {"architecture": "Sedopel", "vocab": 32768, "width": width, "norm": {"eps": 1e-6}, "layers": s_layers}
-    return llama, nafezen, tazadra, sedopel
+    two_maps = {"heads": heads, "kv_heads": heads // 4, "dim": dim // 2, "vdim": dim, "scale": (dim // 2) ** -0.5,
+                "diff": 0.8, "mask": {"size": 1024},
+                "rot": {"base": 500000.0, "dims": dim // 2,
+                        "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    v_moe = {"kind": "moe", "expert": {"ff": ff // (2 * top)}, "shared": {"ff": ff // 2},
+             "router": {"experts": experts, "top": top, "identity": experts // 4,
+                        "groups": {"count": 4, "keep": 2}}}
+    v_layers = [{"type": "attention", "mixer": two_maps, "mlp": dense if i % 2 == 0 else v_moe}
+                for i in range(layers - 2)]
+    selovik = {"architecture": "Selovik", "vocab": 32768, "width": width, "norm": {"eps": 1e-5},
+               "embedding": {"scale": 1.0, "bigram": {"buckets": 8191, "mul_prev": 31, "mul_cur": 17}},
+               "logit_scale": 1.0, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": v_layers}
+    return llama, nafezen, tazadra, sedopel, selovik
 
 
-DESIGN_NAMES = ("llama", "nafezen", "tazadra", "sedopel")
+DESIGN_NAMES = ("llama", "nafezen", "tazadra", "sedopel", "selovik")
 
 
 def profile_steps(args) -> int:
@@ -447,6 +461,7 @@ def compare_designs(args) -> int:
                 engine.release_slot(s)
             print(json.dumps({
                 "design": name, "size": size, "width": engine.spec.hidden_size, "layers": len(engine.spec.layers),
+                "layer_runs": len(engine.spec.schedule),
                 "weights_read_per_token_mb": round(engine.model.parameter_bytes() / 1e6, 1),
                 "weights_read_per_decode_step_mb": round(weight_bytes / 1e6, 1),
                 "prefill": {"tokens": prompt_len, "ms": round(prefill_ms, 3), "tok_s": round(prompt_len / (prefill_ms * 1e-3)),
@@ -483,10 +498,10 @@ def main() -> int:
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="layer sizes: the SmolLM2-135M shape (the benchmark) or a larger one of the family")
     ap.add_argument("--designs", metavar="SIZES", default=None,
-                    help="instead of the benchmark: the Nafezen, Tazadra and Sedopel designs beside the Llama decoder at "
+                    help="instead of the benchmark: the Nafezen, Tazadra, Sedopel and Selovik designs beside the Llama decoder at "
                          "equal width and depth, sizes 's' and/or 'm' with commas: prefill, its parts, decoding")
     ap.add_argument("--only-design", metavar="NAMES", default=None,
-                    help="with --designs: only these of llama, nafezen, tazadra, sedopel (commas between them)")
+                    help="with --designs: only these of llama, nafezen, tazadra, sedopel, selovik (commas between them)")
     ap.add_argument("--profile-steps", type=int, default=0,
                     help="with --designs: run this many eager prompt and decode steps of one design's first "
                          "four layers for a profiler instead of the timed comparison")

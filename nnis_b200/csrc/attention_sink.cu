@@ -144,35 +144,33 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
         const bool is_q = hh < H;
         const int h = is_q ? hh : hh - H;
         const float* src = row + (is_q ? 0 : nq) + (size_t)h * dk;
-        float ss = 0.f;
-        for (int i = lane; i < dk; i += 32) {
-            float x = src[i];
-            const int j = i % sub;  // the place within its map's vector
-            if (j < rot) {
-                int f, other;
-                bool first;
-                if (pairing) {
-                    first = j < half;
-                    f = first ? j : j - half;
-                    other = first ? i + half : i - half;
-                } else {
-                    first = (j & 1) == 0;
-                    f = j >> 1;
-                    other = i ^ 1;
-                }
-                const float ang = p * freq[f];
-                const float c = cosf(ang) * magnitude, s = sinf(ang) * magnitude, y = src[other];
-                x = first ? x * c - y * s : x * c + y * s;
-            }
-            buf[i] = x;
-            ss = fmaf(x, x, ss);
+        // a lane takes a pair of every map: one cosine and one sine serve both of its values
+        for (int t = lane; t < maps * half; t += 32) {
+            const int mp = t / half, f = t - mp * half;
+            const int i0 = mp * sub + (pairing ? f : 2 * f), i1 = pairing ? i0 + half : i0 + 1;
+            float s, c;
+            sincosf(p * freq[f], &s, &c);
+            s *= magnitude;
+            c *= magnitude;
+            const float x0 = src[i0], x1 = src[i1];
+            buf[i0] = x0 * c - x1 * s;
+            buf[i1] = x1 * c + x0 * s;
         }
+        for (int i = lane; i < dk; i += 32)
+            if (i % sub >= rot) buf[i] = src[i];  // (beyond the rotated values of its map)
         float inv = 1.0f;
-        if (norm_heads) inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+        if (norm_heads) {
+            __syncwarp();
+            float ss = 0.f;
+            for (int i = lane; i < dk; i += 32) ss = fmaf(buf[i], buf[i], ss);
+            inv = 1.0f / sqrtf(warp_sum(ss) / (float)dk + eps);
+        }
+        __syncwarp();
         if (is_q && q_scale) inv *= q_scale[h];
         T* dst = is_q ? q_out + (size_t)n * nq + (size_t)h * dk
                       : k_cache + (cache_row + (size_t)h * page_size) * dk;
-        for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(buf[i] * inv);  // (a lane reads what it wrote)
+        for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(buf[i] * inv);
+        __syncwarp();  // (the next head's pairs go to the same place)
     }
     for (int i = threadIdx.x; i < nv; i += 256) {
         const int head = i / dv, within = i - head * dv;

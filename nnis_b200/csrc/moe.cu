@@ -168,23 +168,38 @@ moe_route_choice_kernel(const T* __restrict__ h, const float* __restrict__ wr, c
     }
     const T* x = h + (size_t)n * width;
     const bool by_four = (width & 3) == 0;
-    for (int e = warp; e < outputs; e += 8) {
-        const float* w = wr + (size_t)e * width;
-        float acc = 0.f;
+    // a warp takes four outputs at a time (e, e + 8, e + 16, e + 24): their rows' loads are in flight
+    // together and a loaded piece of x serves all four
+    for (int e0 = warp; e0 < outputs; e0 += 32) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) w[k] = wr + (size_t)min(e0 + 8 * k, outputs - 1) * width;
         if (by_four) {
-#pragma unroll 4
+#pragma unroll 2
             for (int i = lane * 4; i < width; i += 128) {
-                float4 wv = load4(w + i), xv = load4(x + i);
-                acc = fmaf(wv.x, xv.x, acc);
-                acc = fmaf(wv.y, xv.y, acc);
-                acc = fmaf(wv.z, xv.z, acc);
-                acc = fmaf(wv.w, xv.w, acc);
+                const float4 xv = load4(x + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float4 wv = load4(w[k] + i);
+                    acc[k] = fmaf(wv.x, xv.x, acc[k]);
+                    acc[k] = fmaf(wv.y, xv.y, acc[k]);
+                    acc[k] = fmaf(wv.z, xv.z, acc[k]);
+                    acc[k] = fmaf(wv.w, xv.w, acc[k]);
+                }
             }
         } else {
-            for (int i = lane; i < width; i += 32) acc = fmaf(w[i], to_float(x[i]), acc);
+            for (int i = lane; i < width; i += 32) {
+                const float xv = to_float(x[i]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc[k] = fmaf(w[k][i], xv, acc[k]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float sum = warp_sum(acc[k]);
+            if (lane == 0 && e0 + 8 * k < outputs) z[e0 + 8 * k] = sum;
+        }
     }
     __syncthreads();
     if (warp != 0) return;
