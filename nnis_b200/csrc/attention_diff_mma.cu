@@ -22,8 +22,9 @@ constexpr int kDiffRows = 64;   // query rows per CTA
 constexpr int kDiffPage = 64;
 constexpr int kDiffStages = 3;
 
+// (small heads: two CTAs an SM, which caps a thread at 128 registers)
 template <int DK, int DV>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, (DK <= 64 && DV <= 64) ? 2 : 1)
 attn_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                      const int* __restrict__ tiles, const int* __restrict__ seq_first_row,
                      const int* __restrict__ seq_start, const int* __restrict__ seq_count,
