@@ -43,6 +43,7 @@ attn_diff_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     const int hk = h0 / (nq / nkv);
     const int pos = token_pos[n];
     const int dk2 = 2 * dk;
+    constexpr int VB = R <= 2 ? 8 : 4;  // value rows in flight a lane (32 / VB loads of R values each)
     float* qs = q_smem + (size_t)warp * G * dk2;
 
     float m[G][2], l[G][2], acc[G][2][R];
@@ -83,7 +84,7 @@ attn_diff_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     if (by_four) {
-#pragma unroll 4
+#pragma unroll 8
                         for (int i = 0; i < dk; i += 4) {
                             const float4 kv = load4(krow + c * dk + i);
 #pragma unroll
@@ -118,25 +119,31 @@ attn_diff_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 #pragma unroll
                     for (int r = 0; r < R; ++r) acc[g][c][r] *= alpha;
                 }
+            // the value rows of VB keys are asked for together, then added: a row's load waits for none
+            // of the others (keys past the end have weight zero and row 0, which is there to be read)
             const int count = min(32, end - t0);
-#pragma unroll 2
-            for (int j = 0; j < count; ++j) {
-                const int rj = __shfl_sync(0xffffffffu, row_index, j);
-                const T* vrow = v_cache + (size_t)rj * dv;
-                float vr[R];
+            for (int j0 = 0; j0 < count; j0 += VB) {
+                float vr[VB][R];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = lane + 32 * r;
-                    vr[r] = i < dv ? to_float(vrow[i]) : 0.f;
+                for (int u = 0; u < VB; ++u) {
+                    const int rj = __shfl_sync(0xffffffffu, row_index, j0 + u);
+                    const T* vrow = v_cache + (size_t)rj * dv;
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const int i = lane + 32 * r;
+                        vr[u][r] = i < dv ? to_float(vrow[i]) : 0.f;
+                    }
                 }
 #pragma unroll
-                for (int g = 0; g < G; ++g)
+                for (int u = 0; u < VB; ++u)
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const float pj = __shfl_sync(0xffffffffu, p[g][c], j);
+                    for (int g = 0; g < G; ++g)
 #pragma unroll
-                        for (int r = 0; r < R; ++r) acc[g][c][r] = fmaf(pj, vr[r], acc[g][c][r]);
-                    }
+                        for (int c = 0; c < 2; ++c) {
+                            const float pj = __shfl_sync(0xffffffffu, p[g][c], j0 + u);
+#pragma unroll
+                            for (int r = 0; r < R; ++r) acc[g][c][r] = fmaf(pj, vr[u][r], acc[g][c][r]);
+                        }
             }
         }
     }

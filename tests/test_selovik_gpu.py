@@ -239,7 +239,8 @@ def _plain_two_maps(q, k, v, window, scale, lam, post, eps, gate, start=0):
 
 
 @pytest.mark.parametrize("H, G, dk, dv, window", [(4, 2, 16, 24, 9), (6, 3, 24, 40, 50), (3, 3, 10, 34, 64), (5, 1, 18, 6, 1),
-                                                  (8, 1, 12, 40, 70), (2, 1, 64, 128, 0), (8, 2, 32, 200, 65), (2, 2, 130, 8, 300)])
+                                                  (8, 1, 12, 40, 70), (2, 1, 64, 128, 0), (8, 2, 32, 200, 65), (2, 2, 130, 8, 300),
+                                                  (3, 1, 5, 7, 10), (16, 2, 32, 64, 33)])
 def test_attention_with_two_maps_in_every_cut(H, G, dk, dv, window):
     """The attention kernel alone, over a cache whose pages are scattered: a prompt, a later portion
     and single tokens, with the key range whole and in slices, against plain float64."""
@@ -330,7 +331,8 @@ def test_rotation_of_every_map_before_the_cache():
     from nnis_b200.csrc import ops
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(8)
-    for H, G, dk, dv, dims, mag in ((4, 2, 16, 24, 8, 1.2), (3, 1, 10, 6, 10, 1.0), (2, 2, 32, 40, 0, 1.3), (5, 5, 6, 34, 2, 0.9)):
+    for H, G, dk, dv, dims, mag in ((4, 2, 16, 24, 8, 1.2), (3, 1, 10, 6, 10, 1.0), (2, 2, 32, 40, 0, 1.3), (5, 5, 6, 34, 2, 0.9),
+                                    (2, 1, 5, 3, 4, 1.1)):
         n = 70
         rot = {"dims": dims, "base": 100.0}
         f, _ = P.rotation_frequencies(rot) if dims else (torch.zeros(0, dtype=F), 1.0)
@@ -614,7 +616,7 @@ def _random_config(rng):
     n_layers = rng.randint(1, 4)
     for _ in range(n_layers):
         kv = rng.randint(1, 3)
-        dim = rng.choice([2, 6, 8, 10, 16, 24, 32, 40, 64])
+        dim = rng.choice([2, 5, 6, 8, 10, 16, 24, 32, 40, 64])
         dims = rng.choice([0, 2, dim // 2 * 2, (dim // 4) * 2])
         scaling = rng.choice([None, yarn(rng.choice([2.0, 8.0, 32.0]), rng.choice([16, 64, 1024]), rng.choice([4.0, 32.0]),
                                          rng.choice([0.5, 1.0]))])
