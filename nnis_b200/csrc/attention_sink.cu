@@ -144,20 +144,22 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
         const bool is_q = hh < H;
         const int h = is_q ? hh : hh - H;
         const float* src = row + (is_q ? 0 : nq) + (size_t)h * dk;
-        // a lane takes a pair of every map: one cosine and one sine serve both of its values
-        for (int t = lane; t < maps * half; t += 32) {
-            const int mp = t / half, f = t - mp * half;
-            const int i0 = mp * sub + (pairing ? f : 2 * f), i1 = pairing ? i0 + half : i0 + 1;
+        // a lane takes a pair: one cosine and one sine serve both of its values, and every map's pair
+        // of the same place turns by the same angle
+        for (int f = lane; f < half; f += 32) {
             float s, c;
             sincosf(p * freq[f], &s, &c);
             s *= magnitude;
             c *= magnitude;
-            const float x0 = src[i0], x1 = src[i1];
-            buf[i0] = x0 * c - x1 * s;
-            buf[i1] = x1 * c + x0 * s;
+            for (int base = 0; base < dk; base += sub) {
+                const int i0 = base + (pairing ? f : 2 * f), i1 = pairing ? i0 + half : i0 + 1;
+                const float x0 = src[i0], x1 = src[i1];
+                buf[i0] = x0 * c - x1 * s;
+                buf[i1] = x1 * c + x0 * s;
+            }
         }
-        for (int i = lane; i < dk; i += 32)
-            if (i % sub >= rot) buf[i] = src[i];  // (beyond the rotated values of its map)
+        for (int base = 0; base < dk; base += sub)  // (beyond the rotated values of every map)
+            for (int j = rot + lane; j < sub; j += 32) buf[base + j] = src[base + j];
         float inv = 1.0f;
         if (norm_heads) {
             __syncwarp();
@@ -169,7 +171,11 @@ qkv_prep_heads_kernel(const float* __restrict__ a, const float* __restrict__ q_s
         if (is_q && q_scale) inv *= q_scale[h];
         T* dst = is_q ? q_out + (size_t)n * nq + (size_t)h * dk
                       : k_cache + (cache_row + (size_t)h * page_size) * dk;
-        for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(buf[i] * inv);
+        if ((dk & 1) == 0) {  // two values a lane and store (heads start on even places)
+            for (int i = 2 * lane; i < dk; i += 64) store2(dst + i, buf[i] * inv, buf[i + 1] * inv);
+        } else {
+            for (int i = lane; i < dk; i += 32) dst[i] = from_float<T>(buf[i] * inv);
+        }
         __syncwarp();  // (the next head's pairs go to the same place)
     }
     for (int i = threadIdx.x; i < nv; i += 256) {

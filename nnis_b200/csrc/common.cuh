@@ -65,6 +65,12 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
+// Two consecutive elements rounded and stored together; the address must be aligned to two elements.
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(bf16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -142,67 +142,108 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
     for (int s = lane; s < top; s += 32) wt[s] *= inv;
 }
 
-// z: [outputs] scores, then [outputs] choices, then [groups] the runs' best
-template <typename T>
+// A CTA takes TOK tokens.  Shared memory, per token: [outputs] scores, [outputs] choices, [groups] the
+// runs' best.  The logits: with one token a warp takes four outputs at a time (their rows' loads are in
+// flight together); with several tokens a warp takes an output and all the CTA's tokens, so a piece of
+// the router's row is fetched once for all of them.  Then warp k chooses for token k.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(256)
 moe_route_choice_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ correction,
                         const int* __restrict__ token_pos, int* __restrict__ ids, float* __restrict__ weights,
-                        float* __restrict__ pass_weight, int width, int outputs, int experts, int top, int groups,
-                        int keep) {
-    extern __shared__ float z[];
-    float* choice = z + outputs;
-    float* run_best = choice + outputs;
+                        float* __restrict__ pass_weight, int n_tokens, int width, int outputs, int experts, int top,
+                        int groups, int keep) {
+    extern __shared__ float z_all[];
+    const int per = 2 * outputs + groups;
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n = blockIdx.x;
-    int* id = ids + (size_t)n * top;
-    float* wt = weights + (size_t)n * top;
-    if (token_pos[n] < 0) {
-        for (int s = threadIdx.x; s < top; s += 256) {
-            id[s] = -1;
-            wt[s] = 0.f;
-        }
-        if (threadIdx.x == 0) pass_weight[n] = 0.f;
-        return;
-    }
-    const T* x = h + (size_t)n * width;
+    const int n0 = blockIdx.x * TOK;
     const bool by_four = (width & 3) == 0;
-    // a warp takes four outputs at a time (e, e + 8, e + 16, e + 24): their rows' loads are in flight
-    // together and a loaded piece of x serves all four
-    for (int e0 = warp; e0 < outputs; e0 += 32) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* w[4];
+    if (TOK == 1) {
+        const T* x = h + (size_t)n0 * width;
+        for (int e0 = warp; e0 < outputs; e0 += 32) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* w[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) w[k] = wr + (size_t)min(e0 + 8 * k, outputs - 1) * width;
-        if (by_four) {
+            for (int k = 0; k < 4; ++k) w[k] = wr + (size_t)min(e0 + 8 * k, outputs - 1) * width;
+            if (by_four) {
 #pragma unroll 2
-            for (int i = lane * 4; i < width; i += 128) {
-                const float4 xv = load4(x + i);
+                for (int i = lane * 4; i < width; i += 128) {
+                    const float4 xv = load4(x + i);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float4 wv = load4(w[k] + i);
-                    acc[k] = fmaf(wv.x, xv.x, acc[k]);
-                    acc[k] = fmaf(wv.y, xv.y, acc[k]);
-                    acc[k] = fmaf(wv.z, xv.z, acc[k]);
-                    acc[k] = fmaf(wv.w, xv.w, acc[k]);
+                    for (int k = 0; k < 4; ++k) {
+                        const float4 wv = load4(w[k] + i);
+                        acc[k] = fmaf(wv.x, xv.x, acc[k]);
+                        acc[k] = fmaf(wv.y, xv.y, acc[k]);
+                        acc[k] = fmaf(wv.z, xv.z, acc[k]);
+                        acc[k] = fmaf(wv.w, xv.w, acc[k]);
+                    }
+                }
+            } else {
+                for (int i = lane; i < width; i += 32) {
+                    const float xv = to_float(x[i]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc[k] = fmaf(w[k][i], xv, acc[k]);
                 }
             }
-        } else {
-            for (int i = lane; i < width; i += 32) {
-                const float xv = to_float(x[i]);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) acc[k] = fmaf(w[k][i], xv, acc[k]);
+            for (int k = 0; k < 4; ++k) {
+                const float sum = warp_sum(acc[k]);
+                if (lane == 0 && e0 + 8 * k < outputs) z_all[e0 + 8 * k] = sum;
             }
         }
+    } else {
+        const T* x[TOK];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float sum = warp_sum(acc[k]);
-            if (lane == 0 && e0 + 8 * k < outputs) z[e0 + 8 * k] = sum;
+        for (int k = 0; k < TOK; ++k) x[k] = h + (size_t)min(n0 + k, n_tokens - 1) * width;
+        for (int e = warp; e < outputs; e += 8) {
+            const float* w = wr + (size_t)e * width;
+            float acc[TOK];
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) acc[k] = 0.f;
+            if (by_four) {
+#pragma unroll 2
+                for (int i = lane * 4; i < width; i += 128) {
+                    const float4 wv = load4(w + i);
+#pragma unroll
+                    for (int k = 0; k < TOK; ++k) {
+                        const float4 xv = load4(x[k] + i);
+                        acc[k] = fmaf(wv.x, xv.x, acc[k]);
+                        acc[k] = fmaf(wv.y, xv.y, acc[k]);
+                        acc[k] = fmaf(wv.z, xv.z, acc[k]);
+                        acc[k] = fmaf(wv.w, xv.w, acc[k]);
+                    }
+                }
+            } else {
+                for (int i = lane; i < width; i += 32) {
+                    const float wv = w[i];
+#pragma unroll
+                    for (int k = 0; k < TOK; ++k) acc[k] = fmaf(wv, to_float(x[k][i]), acc[k]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < TOK; ++k) {
+                const float sum = warp_sum(acc[k]);
+                if (lane == 0) z_all[k * per + e] = sum;
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    const int n = n0 + warp;
+    if (warp >= TOK || n >= n_tokens) return;
+    float* z = z_all + warp * per;
+    float* choice = z + outputs;
+    float* run_best = choice + outputs;
+    int* id = ids + (size_t)n * top;
+    float* wt = weights + (size_t)n * top;
+    if (token_pos[n] < 0) {
+        for (int s = lane; s < top; s += 32) {
+            id[s] = -1;
+            wt[s] = 0.f;
+        }
+        if (lane == 0) pass_weight[n] = 0.f;
+        return;
+    }
     // one softmax over all outputs
     float mx = -FLT_MAX;
     for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, z[e]);
@@ -442,19 +483,23 @@ NNIS_API int nnis_moe_route_choice(const void* h, const float* wr, const float* 
         !weights || !pass_weight || !token_pos)
         return NNIS_ERR_ARGUMENT;
     if (top > keep * (outputs / groups)) return NNIS_ERR_ARGUMENT;
-    size_t smem = (2 * (size_t)outputs + groups) * sizeof(float);
-    if (smem > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
-    unsigned blocks = (unsigned)n_tokens;
+    const size_t per = (2 * (size_t)outputs + groups) * sizeof(float);
+    if (per > 48 * 1024) return NNIS_ERR_UNSUPPORTED;
+    // many tokens: four a CTA, so a row of the router's matrix is fetched once for four of them
+    const bool several = n_tokens >= 64 && 4 * per <= 48 * 1024;
+    const unsigned blocks = several ? (unsigned)((n_tokens + 3) / 4) : (unsigned)n_tokens;
+    const size_t smem = several ? 4 * per : per;
     cudaError_t e;
+#define NNIS_ROUTE(T, TOK) \
+    launch_dependent(moe_route_choice_kernel<T, TOK>, blocks, 256, smem, stream, (const T*)h, wr, correction, \
+                     token_pos, ids, weights, pass_weight, n_tokens, width, outputs, experts, top, groups, keep)
     if (dtype == NNIS_DTYPE_F32)
-        e = launch_dependent(moe_route_choice_kernel<float>, blocks, 256, smem, stream, (const float*)h, wr,
-                             correction, token_pos, ids, weights, pass_weight, width, outputs, experts, top, groups,
-                             keep);
+        e = several ? NNIS_ROUTE(float, 4) : NNIS_ROUTE(float, 1);
     else if (dtype == NNIS_DTYPE_BF16)
-        e = launch_dependent(moe_route_choice_kernel<bf16>, blocks, 256, smem, stream, (const bf16*)h, wr, correction,
-                             token_pos, ids, weights, pass_weight, width, outputs, experts, top, groups, keep);
+        e = several ? NNIS_ROUTE(bf16, 4) : NNIS_ROUTE(bf16, 1);
     else
         return NNIS_ERR_UNSUPPORTED;
+#undef NNIS_ROUTE
     return e == cudaSuccess ? NNIS_OK : (int)e;
 }
 
