@@ -135,17 +135,23 @@ def route(h, w, p, r, probe=None):
     s = torch.softmax(h @ w[p + ".router"].to(F).T, dim=-1)
     choice = s + w[p + ".correction"].to(F) if (p + ".correction") in w else s.clone()
     groups = r.get("groups")
+    group_gap = torch.full((h.shape[0],), math.inf, dtype=F)
     if groups and int(groups["count"]) > 1:
         count, keep = int(groups["count"]), int(groups["keep"])
         best = choice.view(-1, count, total // count).max(dim=-1).values
         kept = torch.zeros_like(best, dtype=torch.bool)
         kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
         choice = choice.masked_fill(~kept.repeat_interleave(total // count, dim=1), -math.inf)
+        if keep < count:  # how clearly the last group kept beats the first one left out
+            ranked = best.sort(dim=-1, descending=True).values
+            group_gap = ranked[:, keep - 1] - ranked[:, keep]
     ids = choice.topk(int(r["top"]), dim=-1).indices
     if probe is not None:
+        # how clearly the choice was made: the last expert chosen against the first one left out, and the groups
         ordered = choice.sort(dim=-1, descending=True).values
-        probe.setdefault("gaps", []).append(ordered[:, int(r["top"]) - 1] - ordered[:, int(r["top"])]
-                                            if total > int(r["top"]) else torch.full((h.shape[0],), math.inf, dtype=F))
+        gap = ordered[:, int(r["top"]) - 1] - ordered[:, int(r["top"])] if total > int(r["top"]) \
+            else torch.full((h.shape[0],), math.inf, dtype=F)
+        probe.setdefault("gaps", []).append(torch.minimum(gap, group_gap))
     return ids, s.gather(1, ids)
 
 
